@@ -10,3 +10,4 @@ from .registry import (  # noqa: F401
 )
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry  # noqa: F401
 from .qwen2_moe import Qwen2MoeConfig  # noqa: F401  (registers the architecture)
+from .supevik import SupevikConfig  # noqa: F401  (registers the architecture)

@@ -45,10 +45,11 @@ def architecture_name(config: Dict[str, Any]) -> str:
     archs = config.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = config.get("model_type")
-    if isinstance(mt, str):
-        return _ALIASES.get(mt, mt)
-    raise ConfigError("config.json names no architecture (neither 'architectures' nor 'model_type')")
+    for key in ("architecture", "model_type"):
+        mt = config.get(key)
+        if isinstance(mt, str):
+            return _ALIASES.get(mt, mt)
+    raise ConfigError("config.json names no architecture (none of 'architectures', 'architecture', 'model_type')")
 
 
 def lookup(name: str) -> Architecture:

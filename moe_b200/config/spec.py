@@ -32,8 +32,11 @@ class LayerSpec:
     block: str            # registered block arrangement, e.g. "prenorm"
     norm1: PartSpec
     mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    norm2: Optional[PartSpec]
+    ffn: Optional[PartSpec]          # None (with norm2 None): a layer without a feed-forward ("sandwich" only)
+    # norms on the OUTPUT of the mixer and of the feed-forward, before the residual sum ("sandwich")
+    post1: Optional[PartSpec] = None
+    post2: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -48,6 +51,9 @@ class ScheduleEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    # index into ``ModelSpec.joins``: a part that runs right before this layer and mixes the stream
+    # with the embedding output (the start of a pass over a looped stretch of layers)
+    join: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -65,6 +71,8 @@ class ModelSpec:
     max_position_embeddings: Optional[int] = None
     # checkpoint names that may be present but carry no weight of the model
     ignorable: Tuple[str, ...] = ()
+    # parts of category "join" that schedule entries name
+    joins: Tuple[PartSpec, ...] = ()
 
     def cache_entries(self) -> List[int]:
         seen: List[int] = []

@@ -77,6 +77,14 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return t;
 }
 
+// The gate's activation of a gated feed-forward, act(g) * u.
+enum : int { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+__device__ __forceinline__ float glu_mul(int act, float g, float u) {
+    if (act == ACT_GELU_TANH)      // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+        return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return (g / (1.0f + expf(-g))) * u;
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // ---- programmatic dependent launch ------------------------------------------------------

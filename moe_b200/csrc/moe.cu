@@ -404,16 +404,16 @@ route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ 
     }
 }
 
-// act[m, j] = silu(gu[m, j]) * gu[m, inter + j], silu(a) = a / (1 + exp(-a))
-// (reference: src/model.rs:31-33).
+// act[m, j] = f(gu[m, j]) * gu[m, inter + j], f = silu, silu(a) = a / (1 + exp(-a))
+// (reference: src/model.rs:31-33), or another gate activation (glu_mul in common.cuh).
 template <typename OT>
-__global__ void swiglu_kernel(const float* __restrict__ gu, OT* __restrict__ act, long long total, int inter) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, OT* __restrict__ act, long long total, int inter, int f) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long m = i / inter;
     const int j = (int)(i % inter);
     const float a = gu[m * 2 * inter + j], b = gu[m * 2 * inter + inter + j];
-    st_f(act + i, (a / (1.0f + expf(-a))) * b);
+    st_f(act + i, glu_mul(f, a, b));
 }
 
 // One block per token: out[t] = sum_j w[t, j] * y[pos_of_pair[t k + j]] + g[t] * shared[t]
@@ -969,14 +969,14 @@ MOE_API int moe_route_dispatch(const float* logits, const int* seq_of_token, int
                       offsets, sorted_token, pos_of_pair, (const uint4*)x, (uint4*)xs, row_bytes / 16, status);
 }
 
-MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, int inter, cudaStream_t stream) {
+MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, int inter, int f, cudaStream_t stream) {
     const long long total = rows * inter;
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dt == DT_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gu, (float*)act, total, inter);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gu, (float*)act, total, inter, f);
     else
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)act, total, inter);
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)act, total, inter, f);
     return launch_status();
 }
 

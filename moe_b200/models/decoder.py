@@ -26,6 +26,10 @@ def _named_parts(spec: ModelSpec):
     return emb, blocks, final_norm, head
 
 
+def _joins(spec: ModelSpec):
+    return [make_part("join", j) for j in spec.joins]
+
+
 class PartTensors(Mapping):
     """The tensors of one part, by local name, fetched from the store when they are asked for and
     not kept: a part that re-lays its weights out (one slab for all experts, say) holds a tensor of
@@ -63,7 +67,7 @@ def expected_tensors(spec: ModelSpec, store: Optional[WeightStore] = None) -> Di
     that each part finds there (a part may take several, ``Part.tensors_in``)."""
     emb, blocks, final_norm, head = _named_parts(spec)
     out: Dict[str, TensorSpec] = {}
-    parts: List[Part] = [emb, final_norm, head]
+    parts: List[Part] = [emb, final_norm, head] + _joins(spec)
     for b in blocks:
         parts.extend(b.parts())
     for p in parts:
@@ -77,6 +81,10 @@ class DecoderModel:
         self.spec = spec
         self.rt = rt
         self.embedding, self.blocks, self.final_norm, self.head = _named_parts(spec)
+        self.joins = _joins(spec)
+        # a list: every step appends the 32-bit stream after each scheduled layer (a copy, with what
+        # the layer left pending added); for tests and debugging, not under a captured graph
+        self.stream_tap = None
         if check:
             store.check({n: ts.shape for n, ts in expected_tensors(spec, store).items()}, spec.ignorable)
         self._validate_schedule()
@@ -89,6 +97,8 @@ class DecoderModel:
         for b in self.blocks:
             for p in b.parts():
                 bind(p)
+        for j in self.joins:
+            bind(j)
         bind(self.final_norm)
         bind(self.head, embedding=self.embedding)
         self.num_parameters = sum(
@@ -101,6 +111,8 @@ class DecoderModel:
         for i, e in enumerate(self.spec.schedule):
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names layer {e.layer} of {len(self.blocks)}")
+            if e.join is not None and not 0 <= e.join < len(self.joins):
+                raise ValueError(f"schedule entry {i} names join {e.join} of {len(self.joins)}")
             mixer = self.blocks[e.layer].mixer
             own = getattr(mixer, "own_kv", True)
             if e.writes_cache:
@@ -140,8 +152,15 @@ class DecoderModel:
         rt = self.rt
         x = self.embedding.forward(rt, batch.token_ids, batch.num_tokens, batch)
         pending = None
+        for j in self.joins:
+            j.remember(rt, x)
         for e in self.spec.schedule:
+            if e.join is not None:
+                x, pending = self.joins[e.join].forward(rt, x, pending), None
             x, pending = self.blocks[e.layer].forward(rt, x, pending, batch, cache.view(e.cache), cache.state(e.cache))
+            if self.stream_tap is not None:
+                d = pending.materialize(rt) if hasattr(pending, "materialize") else pending
+                self.stream_tap.append(x.clone() if d is None else x + d)
         if batch.num_want == 0:
             return None
         h = self.final_norm.forward(rt, x, delta=delta_for(self.final_norm, pending, rt), rows=batch.want_rows,

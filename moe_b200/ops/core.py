@@ -15,6 +15,8 @@ import torch
 from . import build
 
 DT_F32, DT_BF16 = 0, 1
+# the gate's activation of a gated feed-forward (ACT_* in csrc/common.cuh)
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
 
 
 class KernelError(RuntimeError):
@@ -30,7 +32,10 @@ def lib():
         L = build.load("core")
         P, I, F, LL = c_void_p, c_int, c_float, c_longlong
         sig = {
-            "moe_embed": [P, I, P, P, I, I, I, P, P, P, P, P],
+            "moe_embed": [P, I, P, P, I, I, I, P, P, P, P, F, P],
+            "moe_dyt": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
+            "moe_heads_prepare": [P, I, P, P, P, P, F, P, I, F, I, I, I, I, I, I, P, P, P, I, P, P, P, P, P, I, I, I, I, P, P],
+            "moe_gate_pack": [P, P, I, I, I, I, I, P, I, P],
             "moe_rmsnorm": [P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_rmsnorm_combine": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_add_inplace": [P, P, LL, P],
@@ -49,7 +54,7 @@ def lib():
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
             "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
-            "moe_swiglu": [P, P, I, LL, I, P],
+            "moe_swiglu": [P, P, I, LL, I, I, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
             "moe_sample": [P, I, I, P, P, P, I, F, I, F, F, P, P, P, LL, I, P],
             "moe_logprobs": [P, I, I, P, I, P, P, P, P],
@@ -173,9 +178,9 @@ def check_status(status: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- kernels
-def embed(table, token_ids, out, status, last_token=None, seq_of_token=None, slots=None):
-    """out[t] = table[token_ids[t]]; with ``last_token`` (a per-slot table the sampler fills) a token
-    id of -1 stands for the token sampled last for the row's sequence."""
+def embed(table, token_ids, out, status, last_token=None, seq_of_token=None, slots=None, scale=1.0):
+    """out[t] = table[token_ids[t]] * scale; with ``last_token`` (a per-slot table the sampler fills) a
+    token id of -1 stands for the token sampled last for the row's sequence."""
     _chk(table, "table", dims=2), _chk(token_ids, "token_ids", torch.int32, 1), _chk(out, "out", torch.float32, 2)
     T, H = out.shape
     if token_ids.numel() < T or table.shape[1] != H:
@@ -184,7 +189,7 @@ def embed(table, token_ids, out, status, last_token=None, seq_of_token=None, slo
         _chk(last_token, "last_token", torch.int32, 1), _chk(seq_of_token, "seq_of_token", torch.int32, 1)
         _chk(slots, "slots", torch.int32, 1)
     _ok(lib().moe_embed(_p(table), _dt(table), _p(token_ids), _p(out), T, H, table.shape[0], _p(status),
-                        _p(last_token), _p(seq_of_token), _p(slots), _stream()), "embed")
+                        _p(last_token), _p(seq_of_token), _p(slots), float(scale), _stream()), "embed")
 
 
 def rmsnorm(x, weight, eps, *, delta=None, rows=None, out32=None, out16=None, write_back=True, status=None):
@@ -229,6 +234,102 @@ def rmsnorm_combine(x, cd, weight, eps, *, rows=None, out32=None, out16=None, wr
         return False
     _ok(code, "rmsnorm_combine")
     return True
+
+
+def dyt(x, pre=None, *, delta=None, post=None, rows=None, out32=None, out16=None, write_back=True, status=None):
+    """Dynamic Tanh with the pending residual sum in front of it:
+        x += tanh(pa * delta) * pw + pb   (``post`` = (pa, pw, pb); without it x += delta; stored
+                                           back into ``x`` with ``write_back`` unless ``rows`` selects)
+        out = tanh(a * x) * w + b         (``pre`` = (a, w, b); None: out = x)
+    alpha is a 0-dim float32 tensor on the device.  ``out32`` / ``out16`` may be column slices of wider
+    buffers (unit stride along the row)."""
+    _chk(x, "x", torch.float32, 2)
+    S, H = x.shape
+    n_out = S if rows is None else rows.numel()
+    if delta is not None:
+        _chk(delta, "delta", torch.float32, 2)
+        if delta.shape != x.shape:
+            raise KernelError("dyt: delta shape")
+    elif post is not None:
+        raise KernelError("dyt: a norm after the sublayer needs that sublayer's output")
+    for nm in (pre, post):
+        if nm is not None:
+            a, w, b = nm
+            if a.dtype != torch.float32 or a.numel() != 1 or not a.is_cuda:
+                raise KernelError("dyt: alpha must be one float32 on the device")
+            _chk(w, "weight", torch.float32, 1), _chk(b, "shift", torch.float32, 1)
+            if w.numel() != H or b.numel() != H:
+                raise KernelError("dyt: weight size")
+    if rows is not None:
+        _chk(rows, "rows", torch.int32, 1)
+    ld = None
+    for o, dt in ((out32, torch.float32), (out16, torch.bfloat16)):
+        if o is not None:
+            if not o.is_cuda or o.dtype != dt or o.dim() != 2 or o.stride(1) != 1 or o.shape[0] < n_out or o.shape[1] != H:
+                raise KernelError("dyt: output shape, dtype or layout")
+            if ld is not None and ld != o.stride(0):
+                raise KernelError("dyt: the two outputs must have the same row pitch")
+            ld = o.stride(0)
+    if ld is None:
+        ld = H
+    pa, pw, pb = post if post is not None else (None, None, None)
+    a, w, b = pre if pre is not None else (None, None, None)
+    _ok(lib().moe_dyt(_p(x), _p(delta), _p(pa), _p(pw), _p(pb), _p(a), _p(w), _p(b), _p(rows), _p(out32), _p(out16),
+                      ld, n_out, S, H, 1 if (write_back and rows is None) else 0, _p(status), _stream()), "dyt")
+
+
+def heads_prepare(proj, pos, seq_of_token, *, nh, nkv, d, dv, width, q, k, v, q_norm=None, k_norm=None, eps=0.0,
+                  freq=None, rot=0, mscale=1.0, commit=None, status=None):
+    """From a step's 32-bit projection rows [q heads | k heads | v heads | ...]: per-head RMS norm of
+    queries and keys (``q_norm`` / ``k_norm`` weights of size d, or None), rotation of the first ``rot``
+    dimensions with ``freq`` and cos/sin scaled by ``mscale``, split into q [T, nh, width] and k, v
+    [T, nkv, width], zero-filled beyond d (dv).  ``commit=(view, batch)`` also appends keys and values
+    to that cache layer."""
+    _chk(proj, "proj", torch.float32, 2), _chk(pos, "pos", torch.int32, 1)
+    T = proj.shape[0]
+    for t, n in ((q, nh), (k, nkv), (v, nkv)):
+        _chk(t, "q/k/v")
+        if t.numel() < T * n * width or t.dtype != q.dtype:
+            raise KernelError("heads_prepare: output size or dtype")
+    if proj.shape[1] < (nh + nkv) * d + nkv * dv:
+        raise KernelError("heads_prepare: projection width")
+    for wn in (q_norm, k_norm):
+        if wn is not None:
+            _chk(wn, "head norm weight", torch.float32, 1)
+            if wn.numel() != d:
+                raise KernelError("heads_prepare: head norm weight size")
+    if rot:
+        _chk(freq, "freq", torch.float32, 1)
+        if freq.numel() < rot // 2:
+            raise KernelError("heads_prepare: frequency table too short")
+    kc = vc = se = sl = tb = None
+    ts = ring = ps = npg = 0
+    if commit is not None:
+        view, batch = commit
+        g = view.group
+        if k.dtype != g.dtype or g.num_kv_heads != nkv or g.head_dim != width:
+            raise KernelError("heads_prepare: the cache layer differs from the keys in dtype or shape")
+        kc, vc, se, sl, tb = view.k, view.v, batch.seq_end, batch.slots, g.table
+        ts, ring, ps, npg = g.table.stride(0), g.ring, g.page_size, g.num_pages
+    _ok(lib().moe_heads_prepare(_p(proj), proj.stride(0), _p(pos), _p(seq_of_token), _p(q_norm), _p(k_norm), float(eps),
+                                _p(freq) if rot else None, int(rot), float(mscale), T, nh, nkv, d, dv, width, _p(q),
+                                _p(k), _p(v), _dt(q), _p(kc), _p(vc), _p(se), _p(sl), _p(tb), ts, ring, ps, npg,
+                                _p(status), _stream()), "heads_prepare")
+
+
+def gate_pack(ctx, out, *, nh, dv, width, gate=None):
+    """out[t, h * dv + j] = ctx[t, h, j] * sigmoid(gate[t, h * dv + j]); ``gate``: a column slice
+    [T, nh * dv] of a float32 projection (unit stride along the row), or None for the packing alone."""
+    _chk(ctx, "ctx"), _chk(out, "out", dims=2)
+    T = out.shape[0]
+    if ctx.numel() < T * nh * width or out.shape[1] != nh * dv or out.dtype != ctx.dtype:
+        raise KernelError("gate_pack: shapes or dtypes")
+    ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != (T, nh * dv):
+            raise KernelError("gate_pack: gate shape, dtype or layout")
+        ld = gate.stride(0)
+    _ok(lib().moe_gate_pack(_p(ctx), _p(gate), ld, T, nh, dv, width, _p(out), _dt(out), _stream()), "gate_pack")
 
 
 def add_inplace(a, b):
@@ -491,12 +592,13 @@ def moe_align(topk_idx, num_tokens, top_k, num_experts, offsets, sorted_token, p
                         _p(status), _stream()), "moe_align")
 
 
-def swiglu(gu, act):
+def swiglu(gu, act, fn="silu"):
+    """act = fn(gu[:, :I]) * gu[:, I:]; ``fn`` is one of ``GLU_ACTS``."""
     _chk(gu, "gu", torch.float32, 2), _chk(act, "act", dims=2)
     rows, two_i = gu.shape
     if two_i % 2 or act.shape != (rows, two_i // 2):
         raise KernelError("swiglu: shapes")
-    _ok(lib().moe_swiglu(_p(gu), _p(act), _dt(act), rows, two_i // 2, _stream()), "swiglu")
+    _ok(lib().moe_swiglu(_p(gu), _p(act), _dt(act), rows, two_i // 2, GLU_ACTS[fn], _stream()), "swiglu")
 
 
 def moe_combine(y, pos_of_pair, topk_w, top_k, out, *, shared=None, shared_gate=None):

@@ -31,20 +31,20 @@ def linear(rt, a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor]
     return out
 
 
-def swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(a Wg^T) * (a Wu^T) with w_gate_up = [Wg; Wu] of shape [2 I, K]; returns [M, I] in the
-    compute dtype."""
+def swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(a Wg^T) * (a Wu^T) with w_gate_up = [Wg; Wu] of shape [2 I, K]; returns [M, I] in the
+    compute dtype.  ``act``: the gate's activation, "silu" or "gelu_tanh"."""
     M, inter = a.shape[0], w_gate_up.shape[0] // 2
-    act = torch.empty((M, inter), dtype=rt.compute_dtype, device=a.device)
+    out = torch.empty((M, inter), dtype=rt.compute_dtype, device=a.device)
     if _use_tc(rt, a, w_gate_up):
         from . import tc
 
-        if tc.gemm_tc(a, w_gate_up, act, swiglu=True, status=rt.status):
-            return act
+        if tc.gemm_tc(a, w_gate_up, out, swiglu=True, status=rt.status, act=act):
+            return out
     gu = torch.empty((M, 2 * inter), dtype=torch.float32, device=a.device)
     core.gemm_generic(a, w_gate_up, gu, status=rt.status)
-    core.swiglu(gu, act)
-    return act
+    core.swiglu(gu, out, act)
+    return out
 
 
 def grouped_swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor, group_offsets: torch.Tensor,

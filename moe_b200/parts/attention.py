@@ -8,6 +8,19 @@ kind and an optional sliding window (src/model.rs:689-834, Gqa at :42-50).
 
 A layer with ``own_kv = False`` projects queries only and attends over the cache
 entry another layer wrote.
+
+Options beyond that (each a constant of the part; any of them takes the "prepared" path, whose
+kernel ``heads_prepare`` stands where the rotation-and-split kernel stands otherwise):
+  value_dim   size of a value head dv != head_dim d.  Keys and values are cached in records of one
+              width D >= max(d, dv), zero-filled: zeros add nothing to q . k, and the output columns
+              beyond dv are dropped.  D is also rounded up to a head size the fast kernels take.
+  qk_norm     {"eps": e}: queries and keys are divided by their root mean square over the head,
+              x / sqrt(mean(x^2) + e) * w, with one weight vector for all query heads and one for
+              all key heads, before the rotation.
+  scale       the factor on q . k, instead of 1 / sqrt(d).
+  out_gate    the concatenated heads are multiplied by sigmoid(Wg n), n being the same input as
+              the other projections'; Wg is one more block of rows of the fused projection.
+  a position encoding whose cos and sin carry a factor (``cos_sin_scale``).
 """
 from __future__ import annotations
 
@@ -22,9 +35,21 @@ from ..ops.linear import linear
 from .base import Part, TensorSpec, make_part, register_part
 
 
+def record_width(d: int, dv: int, bf16: bool) -> int:
+    """Width of a cached key/value record for heads of d (queries, keys) and dv (values): in
+    bfloat16 the tensor-core attention takes 64 and 128, everything takes multiples of 16."""
+    m = max(d, dv)
+    if bf16 and m <= 128:
+        return 64 if m <= 64 else 128
+    return -(-m // 16) * 16
+
+
 class GQAttention(Part):
     category, kind = "mixer", "gqa_attention"
     graph_safe = True
+    default_names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                     "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+                     "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "gate_proj.weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -36,36 +61,61 @@ class GQAttention(Part):
         self.bias = bool(p.get("qkv_bias", False))
         self.window = p.get("window")
         self.own_kv = bool(p.get("own_kv", True))
+        self.vd = int(p.get("value_dim") or self.hd)
+        self.qk_norm = p.get("qk_norm")
+        self.out_gate = bool(p.get("out_gate", False))
+        self.fixed_scale = p.get("scale")
         pos = dict(p.get("position") or {"kind": "none"})
         self.position = make_part("position", PartSpec(pos.pop("kind"), pos, spec.prefix))
+        # the prepared path: a kernel of its own between projection and attention, records of width D
+        self.prepared = bool(self.vd != self.hd or self.qk_norm or self.out_gate or self.hd % 16
+                             or self.position.cos_sin_scale() != 1.0)
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if self.hd % 16 or not 16 <= self.hd <= 256:
+        if self.prepared:
+            if not self.own_kv:
+                raise ValueError("a layer that reads another layer's cache takes none of value_dim, qk_norm, out_gate")
+            if not (0 < self.hd <= 256 and 0 < self.vd <= 256):
+                raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels take up to 256")
+        elif self.hd % 16 or not 16 <= self.hd <= 256:
             raise ValueError(f"head_dim {self.hd}: the attention kernels take multiples of 16 from 16 to 256")
         if self.window is not None and self.window <= 0:
             raise ValueError("window must be positive")
+        self.width = self.hd          # of a cached record; the prepared path sets it when bound
 
     def tensors(self):
+        n = self.names
         t = {
-            "q_proj.weight": TensorSpec((self.nh * self.hd, self.hidden)),
-            "o_proj.weight": TensorSpec((self.hidden, self.nh * self.hd)),
+            n["q"]: TensorSpec((self.nh * self.hd, self.hidden)),
+            n["o"]: TensorSpec((self.hidden, self.nh * self.vd)),
         }
         if self.own_kv:
-            t["k_proj.weight"] = TensorSpec((self.nkv * self.hd, self.hidden))
-            t["v_proj.weight"] = TensorSpec((self.nkv * self.hd, self.hidden))
+            t[n["k"]] = TensorSpec((self.nkv * self.hd, self.hidden))
+            t[n["v"]] = TensorSpec((self.nkv * self.vd, self.hidden))
         if self.bias:
-            t["q_proj.bias"] = TensorSpec((self.nh * self.hd,), vector=True)
+            t[n["q_bias"]] = TensorSpec((self.nh * self.hd,), vector=True)
             if self.own_kv:
-                t["k_proj.bias"] = TensorSpec((self.nkv * self.hd,), vector=True)
-                t["v_proj.bias"] = TensorSpec((self.nkv * self.hd,), vector=True)
+                t[n["k_bias"]] = TensorSpec((self.nkv * self.hd,), vector=True)
+                t[n["v_bias"]] = TensorSpec((self.nkv * self.vd,), vector=True)
+        if self.qk_norm:
+            t[n["q_norm"]] = TensorSpec((self.hd,), init="ones", vector=True)
+            t[n["k_norm"]] = TensorSpec((self.hd,), init="ones", vector=True)
+        if self.out_gate:
+            t[n["gate"]] = TensorSpec((self.nh * self.vd, self.hidden))
         t.update(self.position.tensors())
         return t
 
     def kv_request(self):
-        return KVRequest(self.nkv, self.hd, self.window)
+        return KVRequest(self.nkv, self.width, self.window)
 
     def describe(self):
         d = f"GQA({self.nh} q / {self.nkv} kv heads, head_dim={self.hd}{', bias' if self.bias else ''})"
+        if self.vd != self.hd:
+            d += f", value heads of {self.vd}"
+        if self.qk_norm:
+            d += ", q/k RMS norm"
+        if self.out_gate:
+            d += ", sigmoid output gate"
         d += f", {self.position.describe()}"
         if self.window:
             d += f", window {self.window}"
@@ -78,18 +128,82 @@ class GQAttention(Part):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        names = ["q_proj", "k_proj", "v_proj"] if self.own_kv else ["q_proj"]
-        ws = [tensors[n + ".weight"] for n in names]
+        n = self.names
+        roles = ["q", "k", "v"] if self.own_kv else ["q"]
+        ws = [tensors[n[r]] for r in roles]
+        if self.out_gate:
+            ws.append(tensors[n["gate"]])        # the gate's rows ride in the same product
         dt = ws[0].dtype if all(w.dtype == ws[0].dtype for w in ws) else torch.float32
         self.wqkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.bqkv = None
         if self.bias:
-            self.bqkv = torch.cat([tensors[n + ".bias"].to(torch.float32) for n in names]).contiguous()
-        self.wo = tensors["o_proj.weight"].contiguous()
+            bs = [tensors[n[r + "_bias"]].to(torch.float32) for r in roles]
+            if self.out_gate:
+                bs.append(torch.zeros(self.nh * self.vd, dtype=torch.float32, device=bs[0].device))
+            self.bqkv = torch.cat(bs).contiguous()
+        self.wo = tensors[n["o"]].contiguous()
+        self.q_norm_w = self.k_norm_w = None
+        if self.qk_norm:
+            self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
         self.position.bind(tensors, rt)
-        self.scale = self.position.attention_scale() / math.sqrt(self.hd)
+        self.scale = (float(self.fixed_scale) if self.fixed_scale is not None
+                      else self.position.attention_scale() / math.sqrt(self.hd))
+        if self.prepared:
+            self.width = record_width(self.hd, self.vd, rt.is_bf16)
+
+    def _forward_prepared(self, rt, h, batch, cache_view):
+        """Projection (queries, keys, values and gate logits in one product) -> per-head norm,
+        rotation, split and append -> attention over records of width D -> gate and packing ->
+        output projection."""
+        T, D, nh, nkv = batch.num_tokens, self.width, self.nh, self.nkv
+        proj = linear(rt, h.act, self.wqkv, bias=self.bqkv)
+        table, rot = self.position.rotary_table()
+        q = rt.empty((T, nh, D))
+        k_new, v_new = rt.empty((T, nkv, D)), rt.empty((T, nkv, D))
+        ctx = rt.empty((T, nh, D))
+        if getattr(batch, "has_padding", False) and not batch.all_decode:
+            ctx.zero_()      # rows of no sequence are written by no attention kernel
+        # a step of one token a sequence reads its own key from the cache; whole prompts read nothing
+        # from it: both may append at once.  A step that goes on from the cache appends afterwards.
+        early = batch.all_decode or batch.all_fresh
+        core.heads_prepare(proj, batch.pos, batch.seq_of_token, nh=nh, nkv=nkv, d=self.hd, dv=self.vd, width=D, q=q,
+                           k=k_new, v=v_new, q_norm=self.q_norm_w, k_norm=self.k_norm_w,
+                           eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0, freq=table, rot=rot,
+                           mscale=self.position.cos_sin_scale(), commit=(cache_view, batch) if early else None,
+                           status=rt.status)
+        if batch.all_decode:
+            core.attention_decode(q, cache_view, batch, ctx, nh=nh, window=self.window, scale=self.scale,
+                                  status=rt.status)
+        else:
+            done = False
+            if rt.is_bf16:
+                from ..ops import tc
+
+                if batch.all_fresh:
+                    done = tc.attention_prefill(q, k_new, v_new, batch, ctx, nh=nh, nkv=nkv, hd=D, window=self.window,
+                                                scale=self.scale, status=rt.status)
+                else:
+                    done = tc.attention_cached(q, k_new, v_new, cache_view, batch, ctx, nh=nh, window=self.window,
+                                               scale=self.scale, status=rt.status)
+            if not done:
+                kw = dict(nh=nh, window=self.window, scale=self.scale, use_local=True, status=rt.status)
+                if not core.attention_tiled(q, k_new, v_new, cache_view, batch, ctx, **kw):
+                    core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, **kw)
+            if not early:
+                core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
+        if self.out_gate or D != self.vd:
+            packed = rt.empty((T, nh * self.vd))
+            g0 = (nh + nkv) * self.hd + nkv * self.vd
+            core.gate_pack(ctx, packed, nh=nh, dv=self.vd, width=D,
+                           gate=proj[:, g0:g0 + nh * self.vd] if self.out_gate else None)
+        else:
+            packed = ctx.view(T, nh * D)
+        return linear(rt, packed, self.wo)
 
     def forward(self, rt, h, batch, cache_view, state=None):
+        if self.prepared:
+            return self._forward_prepared(rt, h, batch, cache_view)
         T = batch.num_tokens
         nkv = self.nkv if self.own_kv else 0
         qkv = linear(rt, h.act, self.wqkv, bias=self.bqkv)

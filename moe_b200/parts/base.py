@@ -8,6 +8,8 @@ them by the ``kind`` string of the spec.
 
 Interfaces by category
   norm      forward(rt, x, delta=None, rows=None, want32=False, write_back=True) -> Activations
+            normed32(rt, t) -> float32 tensor: the norm of a plain tensor (no residual sum)
+  join      remember(rt, x0); forward(rt, x, pending) -> x: mixes the stream with the embedding output
   position  rotary_table() -> (inv_freq, rotary_dim) or None;  apply(rt, qkv32, layout, positions)
   mixer     forward(rt, h: Activations, batch, cache_view, state) -> delta [T, hidden] float32
             kv_request() -> KVRequest | None;  state_request() -> StateRequest | None
@@ -37,6 +39,19 @@ class LazyDelta:
 
     def materialize(self, rt) -> torch.Tensor:
         raise NotImplementedError
+
+
+class PostNormDelta(LazyDelta):
+    """A sublayer's output that still has to pass a norm of its own before it joins the stream (a
+    block with norms after its sublayers).  Its kind is ``"post_" + norm.kind``; a norm that names that
+    kind forms ``norm(tensor)`` inside its own kernel, in front of the residual sum."""
+
+    def __init__(self, tensor: torch.Tensor, norm):
+        self.tensor, self.norm = tensor, norm
+        self.kind = "post_" + norm.kind
+
+    def materialize(self, rt) -> torch.Tensor:
+        return self.norm.normed32(rt, self.tensor)
 
 
 def delta_for(norm, delta, rt):
@@ -115,9 +130,14 @@ class Part:
     # shape of step is first run with nothing but such rows.
     trace = None
 
+    # local tensor names by role; an architecture whose checkpoint names them otherwise passes
+    # ``names`` (role -> local name) among the part's constants
+    default_names: Dict[str, str] = {}
+
     def __init__(self, spec: PartSpec):
         self.spec = spec
         self.params = dict(spec.params)
+        self.names = {**self.default_names, **dict(self.params.get("names") or {})}
 
     def tensors(self) -> Dict[str, TensorSpec]:
         """Local tensor name -> shape; the checkpoint name is spec.prefix + local name."""

@@ -5,11 +5,16 @@ Pre-norm with two residual sums (src/model.rs:669-684):
 The residual stream ``x`` is float32.  The last sum of a block is left pending
 and folded into the next norm (of the next block, or the final one), which
 reads and writes the stream once instead of twice.
+
+"Sandwich": a norm before AND after each sublayer, and the feed-forward optional:
+    x += post1(mixer(norm1(x)));  x += post2(ffn(norm2(x)))
+A sublayer's output is handed on together with its post-norm (``PostNormDelta``), so the next norm
+before a sublayer may form post-norm, residual sum and its own norm in one kernel.
 """
 from __future__ import annotations
 
 from ..config.spec import LayerSpec
-from .base import delta_for, make_part
+from .base import PostNormDelta, delta_for, make_part
 
 
 class PreNormBlock:
@@ -43,7 +48,37 @@ class PreNormBlock:
         return x, getattr(self.ffn, "forward_lazy", self.ffn.forward)(rt, h, batch)
 
 
-_BLOCKS = {"prenorm": PreNormBlock}
+class SandwichBlock:
+    category, kind = "block", "sandwich"
+
+    def __init__(self, layer: LayerSpec):
+        if layer.post1 is None or (layer.ffn is None) != (layer.norm2 is None) or (layer.ffn is None) != (layer.post2 is None):
+            raise ValueError("a sandwich block has a norm after its mixer, and a feed-forward with both its norms or none")
+        self.layer = layer
+        self.norm1 = make_part("norm", layer.norm1)
+        self.mixer = make_part("mixer", layer.mixer)
+        self.post1 = make_part("norm", layer.post1)
+        self.ffn = self.norm2 = self.post2 = None
+        if layer.ffn is not None:
+            self.norm2 = make_part("norm", layer.norm2)
+            self.ffn = make_part("ffn", layer.ffn)
+            self.post2 = make_part("norm", layer.post2)
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.post1, self.norm2, self.ffn, self.post2) if p is not None]
+
+    def forward(self, rt, x, pending, batch, cache_view, state):
+        h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt),
+                               want32=getattr(self.mixer, "wants32", False))
+        pending = PostNormDelta(self.mixer.forward(rt, h, batch, cache_view, state), self.post1)
+        if self.ffn is None:
+            return x, pending
+        h = self.norm2.forward(rt, x, delta=delta_for(self.norm2, pending, rt),
+                               want32=getattr(self.ffn, "wants32", False))
+        return x, PostNormDelta(self.ffn.forward(rt, h, batch), self.post2)
+
+
+_BLOCKS = {"prenorm": PreNormBlock, "sandwich": SandwichBlock}
 
 
 def register_block(kind: str, cls) -> None:

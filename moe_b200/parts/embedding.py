@@ -16,21 +16,26 @@ from .base import Part, TensorSpec, register_part
 class TokenEmbedding(Part):
     category, kind = "embedding", "token_embedding"
     graph_safe = True
+    default_names = {"weight": "weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(self.params["vocab_size"])
         self.hidden = int(self.params["hidden_size"])
+        self.scale = float(self.params.get("scale", 1.0))   # x = embed[token] * scale
 
     def tensors(self):
-        return {"weight": TensorSpec((self.vocab, self.hidden))}
+        return {self.names["weight"]: TensorSpec((self.vocab, self.hidden))}
+
+    def describe(self):
+        return "token embedding" + (f" x {self.scale:g}" if self.scale != 1.0 else "")
 
     def step_elements(self, num_tokens):
         return float(num_tokens * self.hidden)            # one row a token
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.names["weight"]].contiguous()
 
     def forward(self, rt, token_ids, num_tokens, batch=None):
         """With a batch that carries ``last_token`` (the per-slot table of the tokens sampled last),
@@ -38,15 +43,16 @@ class TokenEmbedding(Part):
         x = rt.empty((num_tokens, self.hidden), torch.float32)
         last = getattr(batch, "last_token", None)
         if last is not None:
-            core.embed(self.weight, token_ids, x, rt.status, last, batch.seq_of_token, batch.slots)
+            core.embed(self.weight, token_ids, x, rt.status, last, batch.seq_of_token, batch.slots, scale=self.scale)
         else:
-            core.embed(self.weight, token_ids, x, rt.status)
+            core.embed(self.weight, token_ids, x, rt.status, scale=self.scale)
         return x
 
 
 class LMHead(Part):
     category, kind = "head", "lm_head"
     graph_safe = True
+    default_names = {"weight": "weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -55,7 +61,7 @@ class LMHead(Part):
         self.tied = bool(self.params.get("tied", False))
 
     def tensors(self):
-        return {} if self.tied else {"weight": TensorSpec((self.vocab, self.hidden))}
+        return {} if self.tied else {self.names["weight"]: TensorSpec((self.vocab, self.hidden))}
 
     def describe(self):
         return "output projection" + (" (the embedding)" if self.tied else "")
@@ -65,12 +71,63 @@ class LMHead(Part):
 
     def bind(self, tensors, rt, embedding: TokenEmbedding = None):
         super().bind(tensors, rt)
-        self.weight = embedding.weight if self.tied else tensors["weight"].contiguous()
+        self.weight = embedding.weight if self.tied else tensors[self.names["weight"]].contiguous()
 
     def forward(self, rt, h):
         """h: Activations of the wanted rows -> logits [rows, vocab] float32."""
         return linear(rt, h.act, self.weight)
 
 
+class ConcatLinearJoin(Part):
+    """x <- W [x; x0]: the stream is joined with the embedding output x0 and projected back to the
+    model's width (W: [hidden, 2 hidden], the stream's columns first).  A model that runs a stretch of
+    its layers several times does this at the start of every pass.  The two halves share one buffer
+    in the compute dtype, whose right half is filled once per step (``remember``); the left half
+    takes the stream with whatever was still pending, in the kernel of the norm that would have
+    added it."""
+
+    category, kind = "join", "concat_linear"
+    graph_safe = True
+    lazy_kinds = ("post_dyt",)
+    default_names = {"weight": "weight"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.params["hidden_size"])
+
+    def tensors(self):
+        return {self.names["weight"]: TensorSpec((self.hidden, 2 * self.hidden))}
+
+    def describe(self):
+        return "join with the embedding output, projected 2:1"
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors[self.names["weight"]].contiguous()
+        self._both = None
+
+    def _halves(self, rt):
+        return self.hidden, ("out16" if rt.is_bf16 else "out32")
+
+    def remember(self, rt, x0):
+        H, key = self._halves(rt)
+        self._both = rt.empty((x0.shape[0], 2 * H))
+        core.dyt(x0, None, write_back=False, status=rt.status, **{key: self._both[:, H:]})
+
+    def forward(self, rt, x, pending):
+        from .base import LazyDelta
+
+        H, key = self._halves(rt)
+        post = None
+        if isinstance(pending, LazyDelta):
+            if pending.kind == "post_dyt":
+                post, pending = pending.norm.triple(), pending.tensor
+            else:
+                pending = pending.materialize(rt)
+        core.dyt(x, None, delta=pending, post=post, write_back=False, status=rt.status, **{key: self._both[:, :H]})
+        return linear(rt, self._both, self.weight)
+
+
+register_part("join", "concat_linear", ConcatLinearJoin)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -24,32 +24,40 @@ def _fuse_rows(tensors):
 
 
 class DenseSwiGLU(Part):
+    """y = Wd (act(Wg n) * (Wu n)); ``activation`` is "silu" (the default) or "gelu_tanh"."""
+
     category, kind = "ffn", "dense_swiglu"
     graph_safe = True
     wants32 = False
+    default_names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(self.params["hidden_size"])
         self.size = int(self.params["size"])
+        self.activation = str(self.params.get("activation", "silu"))
+        if self.activation not in core.GLU_ACTS:
+            raise ValueError(f"dense gated feed-forward: activation '{self.activation}' is none of {sorted(core.GLU_ACTS)}")
 
     def tensors(self):
+        n = self.names
         return {
-            "gate_proj.weight": TensorSpec((self.size, self.hidden)),
-            "up_proj.weight": TensorSpec((self.size, self.hidden)),
-            "down_proj.weight": TensorSpec((self.hidden, self.size)),
+            n["gate"]: TensorSpec((self.size, self.hidden)),
+            n["up"]: TensorSpec((self.size, self.hidden)),
+            n["down"]: TensorSpec((self.hidden, self.size)),
         }
 
     def describe(self):
-        return f"dense SwiGLU {self.size}"
+        return f"dense {'SwiGLU' if self.activation == 'silu' else 'gated ' + self.activation} {self.size}"
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.w_gu = _fuse_rows([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        n = self.names
+        self.w_gu = _fuse_rows([tensors[n["gate"]], tensors[n["up"]]])
+        self.w_down = tensors[n["down"]].contiguous()
 
     def forward(self, rt, h, batch):
-        return linear(rt, swiglu_linear(rt, h.act, self.w_gu), self.w_down)
+        return linear(rt, swiglu_linear(rt, h.act, self.w_gu, self.activation), self.w_down)
 
 
 class CombineDelta(LazyDelta):

@@ -1,4 +1,8 @@
-"""RMSNorm: s = 1/sqrt(mean(x^2) + eps), out = x * s * w (src/model.rs:211-216)."""
+"""Norms of the residual stream.
+
+RMSNorm: s = 1/sqrt(mean(x^2) + eps), out = x * s * w (src/model.rs:211-216).
+DynamicTanh: out = tanh(alpha x) * w + b with a scalar alpha; no statistic of x enters.
+Both add a pending delta to the 32-bit stream inside their kernel before they normalise it."""
 from __future__ import annotations
 
 import torch
@@ -33,6 +37,11 @@ class RMSNorm(Part):
         super().bind(tensors, rt)
         self.weight = tensors["weight"].to(torch.float32).contiguous()
 
+    def normed32(self, rt, t):
+        out = rt.empty(t.shape, torch.float32)
+        core.rmsnorm(t, self.weight, self.eps, out32=out, write_back=False, status=rt.status)
+        return out
+
     def forward(self, rt, x, delta=None, rows=None, want32=False, write_back=True) -> Activations:
         """Normalise ``x (+ delta)``; with ``delta`` the sum is written back into ``x``
         (unless ``rows`` selects a subset, which leaves ``x`` alone)."""
@@ -56,4 +65,63 @@ class RMSNorm(Part):
         return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
 
 
+class DynamicTanh(Part):
+    """tanh(alpha * x) * weight + shift.  Where the delta it is handed is the output of a sublayer
+    that has a Dynamic Tanh of its own in front of the residual sum (``PostNormDelta`` of kind
+    ``post_dyt``), both norms and the sum are one kernel."""
+
+    category, kind = "norm", "dyt"
+    graph_safe = True
+    lazy_kinds = ("post_dyt",)
+    default_names = {"weight": "weight", "shift": "bias", "alpha": "alpha"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(self.params["size"])
+
+    def tensors(self):
+        n = self.names
+        return {n["weight"]: TensorSpec((self.size,), init="ones", vector=True),
+                n["shift"]: TensorSpec((self.size,), init="zeros", vector=True),
+                n["alpha"]: TensorSpec((), init="ones", vector=True)}
+
+    def describe(self):
+        return "Dynamic Tanh"
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        n = self.names
+        self.weight = tensors[n["weight"]].to(torch.float32).contiguous()
+        self.shift = tensors[n["shift"]].to(torch.float32).contiguous()
+        self.alpha = tensors[n["alpha"]].to(torch.float32).reshape(()).contiguous()
+
+    def triple(self):
+        return self.alpha, self.weight, self.shift
+
+    def normed32(self, rt, t):
+        out = rt.empty(t.shape, torch.float32)
+        core.dyt(t, self.triple(), out32=out, write_back=False, status=rt.status)
+        return out
+
+    def forward(self, rt, x, delta=None, rows=None, want32=False, write_back=True) -> Activations:
+        n = x.shape[0] if rows is None else rows.numel()
+        out32 = out16 = None
+        if rt.is_bf16:
+            out16 = rt.empty((n, self.size), torch.bfloat16)
+            if want32:
+                out32 = rt.empty((n, self.size), torch.float32)
+        else:
+            out32 = rt.empty((n, self.size), torch.float32)
+        post = None
+        if isinstance(delta, LazyDelta):
+            if delta.kind == "post_dyt":
+                post, delta = delta.norm.triple(), delta.tensor
+            else:
+                delta = delta.materialize(rt)
+        core.dyt(x, self.triple(), delta=delta, post=post, rows=rows, out32=out32, out16=out16, write_back=write_back,
+                 status=rt.status)
+        return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dyt", DynamicTanh)

@@ -6,6 +6,8 @@ inv_freq[i] (src/model.rs:326-328).  Pairs are half-split: (i, i + dim/2).
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import Part, register_part
@@ -44,6 +46,53 @@ class RotaryEncoding(Part):
         """Extra factor on 1/sqrt(head_dim); 1 without context extension (src/spec.rs:148-151)."""
         return 1.0
 
+    def cos_sin_scale(self) -> float:
+        """Factor on both cos and sin; 1 without context extension."""
+        return 1.0
+
+
+class YarnRotary(RotaryEncoding):
+    """Rotary encoding with YaRN context extension.  With r rotated dimensions, base theta and
+    f_i = theta^(-2i/r), let turn(t) = r ln(original / (2 pi t)) / (2 ln theta) be the (fractional)
+    pair that makes t turns over the original context, lo = max(floor(turn(fast)), 0),
+    hi = min(ceil(turn(slow)), r - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1).  Pair i
+    turns at f_i / factor * ramp_i + f_i (1 - ramp_i): fast pairs keep their frequency, slow ones are
+    interpolated.  cos and sin are multiplied by 0.1 ln(factor) + 1.  The table is formed in float64
+    and rounded to float32 once."""
+
+    kind = "rotary_yarn"
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.factor, self.original = float(p["factor"]), float(p["original"])
+        self.fast, self.slow = float(p["fast"]), float(p["slow"])
+        if self.factor <= 0 or self.original <= 0 or self.fast <= 0 or self.slow <= 0 or self.theta <= 1:
+            raise ValueError("rotary_yarn: factor, original, fast and slow must be positive and theta > 1")
+
+    def frequencies(self) -> torch.Tensor:
+        r = self.rotary_dim
+        i = torch.arange(r // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / r)
+
+        def turn(t):
+            return r * math.log(self.original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(turn(self.fast)), 0)
+        hi = min(math.ceil(turn(self.slow)), r - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return (f / self.factor * ramp + f * (1.0 - ramp)).to(torch.float32)
+
+    def bind(self, tensors, rt):
+        Part.bind(self, tensors, rt)
+        self.inv_freq = self.frequencies().to(rt.device)
+
+    def describe(self):
+        return f"rope theta {self.theta:.0f} on {self.rotary_dim} dims, YaRN x{self.factor:g} from {self.original:g}"
+
+    def cos_sin_scale(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0
+
 
 class NoPositionEncoding(Part):
     category, kind = "position", "none"
@@ -57,6 +106,10 @@ class NoPositionEncoding(Part):
     def attention_scale(self) -> float:
         return 1.0
 
+    def cos_sin_scale(self) -> float:
+        return 1.0
+
 
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "rotary_yarn", YarnRotary)
 register_part("position", "none", NoPositionEncoding)
