@@ -477,6 +477,162 @@ def profile_step(args):
     return 0
 
 
+# Supevik at sizes that resemble a real model's layers, and beside each the library's closest model at
+# equal size: Qwen2 MoE without experts (dense SwiGLU layers), as many layers as the Supevik shape has
+# layer RUNS, the same width, heads, head size, feed-forward size, window and vocabulary.
+SUPEVIK_SHAPES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ff=5632, window=1024, rot=64, layers=6,
+                  loop=(1, 5, 2), vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, ff=11008, window=2048, rot=64, layers=4,
+                  loop=(0, 4, 2), vocab=32768),
+}
+
+
+def supevik_config(sh):
+    mixer = {"heads": sh["heads"], "kv_heads": sh["kv_heads"], "dim": sh["dim"], "vdim": sh["vdim"],
+             "scale": sh["dim"] ** -0.5, "mask": {"size": sh["window"]},
+             "rot": {"dims": sh["rot"], "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    a, b, t = sh["loop"]
+    return {"architecture": "Supevik", "vocab": sh["vocab"], "width": sh["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "loop": {"start": a, "stop": b, "times": t},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": sh["ff"]}}] * sh["layers"]}
+
+
+def dense_qwen_config(sh):
+    a, b, t = sh["loop"]
+    runs = sh["layers"] + (b - a) * (t - 1)
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=runs,
+                hidden_size=sh["width"], num_attention_heads=sh["heads"], num_key_value_heads=sh["kv_heads"],
+                head_dim=sh["dim"], num_experts=0, intermediate_size=sh["ff"], vocab_size=sh["vocab"], rope_theta=1e6,
+                rms_norm_eps=1e-5, use_sliding_window=True, sliding_window=sh["window"], max_window_layers=0,
+                tie_word_embeddings=False, max_position_embeddings=8192, qkv_bias=True)
+
+
+def _median_ms(fn, reps=5, warmup=3):
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]
+
+
+def supevik_kernels(sh, pk):
+    """The new design's own kernels beside the like kernels of the closest model, each alone at 8,192
+    tokens (what a call reads and writes exceeds L2), as a fraction of the measured copy bandwidth
+    (products: of the measured bf16 peak)."""
+    import torch
+
+    from moe_b200.ops import core, tc
+
+    dev = "cuda:0"
+    T, H, nh, nkv, d, I = 8192, sh["width"], sh["heads"], sh["kv_heads"], sh["dim"], sh["ff"]
+    status = core.new_status(dev)
+    r = lambda *s: torch.randn(*s, device=dev)
+    x, delta, w, b, al = r(T, H), r(T, H), r(H), r(H), torch.tensor(0.8, device=dev)
+    o16 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    out = {}
+
+    def row(name, ms, nbytes=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if nbytes:
+            e["gb_s"] = round(nbytes / ms / 1e6, 0)
+            e["of_copy_peak"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tflops"] = round(flops / ms / 1e9, 0)
+            e["of_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+        out[name] = e
+
+    nb = T * H * (4 + 4 + 4 + 2)
+    row("dyt (norm after + sum + norm before)", _median_ms(lambda: core.dyt(x, (al, w, b), delta=delta, post=(al, w, b), out16=o16, status=status)), nb)
+    row("rmsnorm (sum + norm)", _median_ms(lambda: core.rmsnorm(x, w, 1e-5, delta=delta, out16=o16, status=status)), nb)
+    wq = (nh + 2 * nkv) * d
+    proj = r(T, wq + nh * d)
+    qkv = r(T, wq)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    q, k, v = (torch.empty((T, n, d), dtype=torch.bfloat16, device=dev) for n in (nh, nkv, nkv))
+    freq = torch.rand(sh["rot"] // 2, device=dev)
+    nb = T * wq * (4 + 2)
+    row("heads_prepare (q/k norm + rotation + split)", _median_ms(lambda: core.heads_prepare(
+        proj, pos, seq, nh=nh, nkv=nkv, d=d, dv=d, width=d, q=q, k=k, v=v, q_norm=w[:d].contiguous(), k_norm=b[:d].contiguous(),
+        eps=1e-5, freq=freq, rot=sh["rot"], mscale=1.1, status=status)), nb)
+    row("rope_split (rotation + split)", _median_ms(lambda: core.rope_split(qkv, pos, freq, nh, nkv, d, sh["rot"], q, k, v)), nb)
+    ctx = torch.empty((T, nh, d), dtype=torch.bfloat16, device=dev)
+    packed = torch.empty((T, nh * d), dtype=torch.bfloat16, device=dev)
+    row("gate_pack (sigmoid gate on the heads)", _median_ms(lambda: core.gate_pack(ctx, packed, nh=nh, dv=d, width=d, gate=proj[:, wq:])),
+        T * nh * d * (2 + 4 + 2))
+    a16 = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    wgu = (torch.randn(2 * I, H, device=dev) / 32).to(torch.bfloat16)
+    act = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
+    fl = 2.0 * T * 2 * I * H
+    row("gate|up product, gelu_tanh epilogue", _median_ms(lambda: tc.gemm_tc(a16, wgu, act, swiglu=True, status=status, act="gelu_tanh")), flops=fl)
+    row("gate|up product, silu epilogue", _median_ms(lambda: tc.gemm_tc(a16, wgu, act, swiglu=True, status=status)), flops=fl)
+    core.check_status(status)
+    return out
+
+
+def run_supevik(args):
+    """``--workload supevik``: prefill and decode of the Supevik design at two sizes, the closest existing
+    model at equal size beside it, and the new kernels beside their counterparts.  One JSON line per
+    shape; not the benchmark record."""
+    import torch
+
+    import moe_b200
+
+    pk = peaks()
+    names = [args.shape] if args.shape in SUPEVIK_SHAPES else list(SUPEVIK_SHAPES)
+    for name in names:
+        sh = SUPEVIK_SHAPES[name]
+        V = sh["vocab"]
+        res = {"workload": "supevik", "shape": name, "sizes": sh, "dtype": "bfloat16", "data": "synthetic, random weights",
+               "peaks": pk}
+        for label, cfg in (("supevik", supevik_config(sh)), ("qwen2_dense", dense_qwen_config(sh))):
+            model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            r = {"parameters": int(model.num_parameters)}
+            eng = moe_b200.Engine(model, max_tokens=64 * (512 + args.steps + 64) + 4096, max_slots=64)
+            ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
+
+            def prefill():
+                s = eng.new_sequence()
+                eng.step([s], [ids], check=False)
+                eng.release(s)
+
+            ms = _median_ms(prefill)
+            r["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3, 0)}
+            for B in (1, 8, 64):
+                slots = [eng.new_sequence() for _ in range(B)]
+                eng.step(slots, [ids[:PROMPT_LEN]] * B, check=False)
+                for i in range(args.warmup):
+                    eng.step(slots, [[i % V]] * B, check=False)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for i in range(args.steps):
+                    eng.step(slots, [[(i + 5) % V]] * B, check=False)
+                b.record()
+                torch.cuda.synchronize()
+                eng.rt.check()
+                ms = a.elapsed_time(b) / args.steps
+                r[f"decode_b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 0)}
+                for s in slots:
+                    eng.release(s)
+            res[label] = r
+            del eng, model
+            torch.cuda.empty_cache()
+        res["kernels_at_8192_tokens"] = supevik_kernels(sh, pk)
+        print(json.dumps(res), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -490,11 +646,13 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="with --profile-step: the path whose kernels are wanted")
-    ap.add_argument("--shape", choices=["a2.7b", "57b"], default="a2.7b", help="with --sweep: the layer sizes")
+    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(SUPEVIK_SHAPES), default="a2.7b",
+                    help="with --sweep: the layer sizes; with --workload supevik: one of its shapes (default: all)")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
-    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt"], default=None,
+    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik"], default=None,
                     help="fp32-32k: the true 32-bit path at a context of 32,768; long-prompt: one bfloat16 prompt of "
-                         "--prompt-len tokens [32768] run in pieces (each prints its own line, no benchmark record)")
+                         "--prompt-len tokens [32768] run in pieces; supevik: the Supevik design at two sizes beside the "
+                         "closest model at equal size (each prints its own line, no benchmark record)")
     ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
@@ -513,6 +671,8 @@ def main():
         return run_long_prompt(args)
     if args.workload == "fp32-32k":
         return run_fp32_long(args)
+    if args.workload == "supevik":
+        return run_supevik(args)
     return run_ours(args)
 
 

@@ -163,9 +163,15 @@ def summary(model) -> str:
     n = len(model.blocks)
     lines = [spec.architecture, f"  layers {n}  hidden {spec.hidden_size}  vocab {spec.vocab_size}"]
     if len(spec.schedule) != n or any(e.layer != i for i, e in enumerate(spec.schedule)):
+        # (a layer run after a join is marked "+"; a cache entry is named where it is not the layer's number)
         lines.append("  schedule   " + " ".join(
-            f"{e.layer}" + ("" if e.writes_cache and e.cache == e.layer else f"[cache {e.cache}{'' if e.writes_cache else ', read'}]")
+            ("+" if e.join is not None else "") + f"{e.layer}"
+            + ("" if e.writes_cache and e.cache == e.layer else f"[cache {e.cache}{'' if e.writes_cache else ', read'}]")
             for e in spec.schedule))
+    if model.embedding.describe() != model.embedding.kind:
+        lines.append(f"  {'embedding':<10} {model.embedding.describe()}")
+    for j in getattr(model, "joins", []):
+        lines.append(f"  {'join (+)':<10} {j.describe()}")
     by_category: Dict[str, List[str]] = {}
     for b in model.blocks:
         for part in b.parts():

@@ -86,7 +86,36 @@ struct FusedArgs {
     void* v_append;
     void* out;               // [T, nh * hd]
     int* tickets;            // [T * nkv], zero before and after the launch
+    const float* gate;       // with dv > 0: 32-bit gate logits [T, gate_ld], head h at columns h * dv ..; or null
+    int gate_ld;
+    int dv;                  // > 0: out is [T, nh * dv], the first dv columns of every head (times sigmoid(gate))
 };
+
+// Where the merge of the splits writes a head's column d: the plain output [T, nh, hd], or, for
+// layers whose value heads are narrower than the cached records or that gate their heads, the packed
+// output [T, nh, dv] with the sigmoid of the gate logit multiplied in.  The head's value is rounded
+// through the storage type first, as a prompt's attention kernel stores it before its gate kernel
+// reads it: a token decoded alone and the same token inside a prompt then round at the same places.
+struct GateOut {
+    const float* gate;
+    int gate_ld;
+    int dv;
+};
+template <typename T>
+__device__ __forceinline__ void write_head_column(T* out, const GateOut go, int t, int nh, int h, int hd, int d,
+                                                  float val) {
+    if (go.dv <= 0) {
+        st_f(out + ((size_t)t * nh + h) * hd + d, val);
+        return;
+    }
+    if (d >= go.dv) return;
+    if (go.gate) {
+        T r;
+        st_f(&r, val);
+        val = ld_f(&r) * (1.0f / (1.0f + expf(-go.gate[(size_t)t * go.gate_ld + (size_t)h * go.dv + d])));
+    }
+    st_f(out + ((size_t)t * nh + h) * go.dv + d, val);
+}
 
 // EPC consecutive elements d0 .. of one head's 32-bit row, rotated (same arithmetic as
 // rope_commit_kernel) and rounded through the storage type.  ang: cos[half], sin[half].
@@ -175,7 +204,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     if (s < 0) {                                         // padding row: zeros (unfused: by the merge kernel)
         if (FUSED && split == 0 && h0 == 0)
             for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
-                st_f((T*)fa.out + ((size_t)t * nh + (size_t)kvh * group) * HD + i, 0.f);
+                write_head_column((T*)fa.out, GateOut{nullptr, 0, fa.dv}, t, nh, kvh * group + i / HD, HD, i % HD, 0.f);
         return;
     }
     if (FUSED) __syncthreads();
@@ -372,7 +401,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
             ll += f * __ldcg(base + (size_t)sp * REC + HD + 1);
             a += f * __ldcg(base + (size_t)sp * REC + d);
         }
-        st_f((T*)fa.out + ((size_t)t * nh + h) * HD + d, a / ll);
+        write_head_column((T*)fa.out, GateOut{fa.gate, fa.gate_ld, fa.dv}, t, nh, h, HD, d, a / ll);
     }
 }
 
@@ -516,13 +545,14 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 // one block per (token, head): merge the splits in order and normalise
 template <typename T>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                         const int* __restrict__ seq_of_token, int nh, int hd, int nsplit) {
+                                         const int* __restrict__ seq_of_token, int nh, int hd, int nsplit,
+                                         const GateOut go) {
     pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const int rec = hd + 2;
-    T* o = out + ((size_t)t * nh + h) * hd;
     if (seq_of_token[t] < 0) {
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) st_f(o + d, 0.f);
+        for (int d = threadIdx.x; d < hd; d += blockDim.x)
+            write_head_column(out, GateOut{nullptr, 0, go.dv}, t, nh, h, hd, d, 0.f);
         return;
     }
     const float* base = partial + ((size_t)t * nh + h) * nsplit * rec;
@@ -539,7 +569,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* _
             const float ms = base[(size_t)s * rec + hd];
             if (ms != -INFINITY) a += expf(ms - mm) * base[(size_t)s * rec + d];
         }
-        st_f(o + d, a / ll);
+        write_head_column(out, go, t, nh, h, hd, d, a / ll);
     }
 }
 
@@ -561,7 +591,7 @@ template <typename T>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
            const int* seq_of_token, const int* pos, const int* slots, const int* tables, int table_stride, int ring,
            int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
-           int* status, cudaStream_t stream, const FusedArgs* fused = nullptr) {
+           int* status, cudaStream_t stream, const FusedArgs* fused = nullptr, const GateOut go = GateOut{nullptr, 0, 0}) {
     const int group = nh / nkv;
     dim3 grid(nsplit, nkv, num_tokens);
     const int row_bytes = hd * (int)sizeof(T);
@@ -612,7 +642,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
 #undef FAST_G
     if (fused || rc) return rc;
     return launch_pdl(attn_decode_merge_kernel<T>, dim3(num_tokens, nh), 128, 0, stream, (const float*)partial, (T*)out,
-                      seq_of_token, nh, hd, nsplit);
+                      seq_of_token, nh, hd, nsplit, go);
 }
 
 }  // namespace
@@ -628,15 +658,17 @@ MOE_API int moe_attention_decode_fused(const float* qkv, const float* inv_freq, 
                                        void* out, float* partial, int* tickets, int dt, const int* seq_of_token,
                                        const int* pos, const int* slots, const int* tables, int table_stride,
                                        int ring, int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd,
-                                       int window, float scale, int nsplit, int* status, cudaStream_t stream) {
+                                       int window, float scale, int nsplit, const float* gate, int gate_ld, int dv,
+                                       int* status, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nsplit < 1 || nsplit > 65535 ||
-        nkv > 65535 || num_tokens > 65535 || rot < 0 || rot > hd || (rot & 1) || (rot > 0 && !inv_freq) || !tickets)
+        nkv > 65535 || num_tokens > 65535 || rot < 0 || rot > hd || (rot & 1) || (rot > 0 && !inv_freq) || !tickets ||
+        dv < 0 || dv > hd || (gate && dv == 0))
         return (int)cudaErrorInvalidValue;
     if (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16) return -1;
     FusedArgs fa;
     fa.qkv = qkv, fa.inv_freq = inv_freq, fa.rot = rot, fa.k_append = k_cache, fa.v_append = v_cache, fa.out = out;
-    fa.tickets = tickets;
+    fa.tickets = tickets, fa.gate = gate, fa.gate_ld = gate_ld, fa.dv = dv;
     if (dt == DT_F32)
         return launch<float>(nullptr, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride,
                              ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status,
@@ -647,12 +679,16 @@ MOE_API int moe_attention_decode_fused(const float* qkv, const float* inv_freq, 
 }
 
 // q: [T, nh, hd]; out: [T, nh * hd]; partial: T * nh * nsplit * (hd + 2) floats of scratch.
+// With dv > 0 out is [T, nh * dv]: the first dv columns of every head, times the sigmoid of the
+// 32-bit gate logits gate[t * gate_ld + h * dv + d] if gate is given.
 MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
                                  int dt, const int* seq_of_token, const int* pos, const int* slots,
                                  const int* tables, int table_stride, int ring, int page_size, int num_pages,
                                  int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
-                                 int* status, cudaStream_t stream) {
+                                 const float* gate, int gate_ld, int dv, int* status, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
+    if (dv < 0 || dv > hd || (gate && dv == 0)) return (int)cudaErrorInvalidValue;
+    const GateOut go{gate, gate_ld, dv};
     if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh <= 0 || nh > 65535 || nh % nkv != 0 || nsplit < 1 ||
         nsplit > 65535 || nkv > 65535 || num_tokens > 65535 || !q || !k_cache || !v_cache || !out || !partial)
         return (int)cudaErrorInvalidValue;
@@ -661,10 +697,11 @@ MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void*
         return (int)cudaErrorInvalidValue;
     if (dt == DT_F32)
         return launch<float>(q, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride, ring,
-                             page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status, stream);
+                             page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status, stream,
+                             nullptr, go);
     return launch<__nv_bfloat16>(q, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride,
                                  ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status,
-                                 stream);
+                                 stream, nullptr, go);
 }
 
 // ---- the entry point that allocates nothing (see attention_decode_noalloc.h) -----------------

@@ -26,109 +26,197 @@ struct PrepCommit {
     int table_stride, ring, page_size, num_pages;
 };
 
-constexpr int PREP_WARPS = 4;
+constexpr int PREP_WARPS = 8;
 
-template <typename OT>
+__device__ __forceinline__ void prep_store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void prep_store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// A block takes PREP_WARPS heads of one token (grid: tokens x groups of heads): the token's angles
+// once a block (cos and sin of pos * freq[i], times mscale) in shared memory, then a warp per head:
+// load (four elements a lane where the sizes allow, VEC), sum of squares over the warp, scale,
+// rotate through a per-warp buffer, store.
+template <typename OT, bool VEC>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restrict__ pos,
                      const int* __restrict__ seq_of_token, const float* __restrict__ q_norm,
                      const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot,
                      float mscale, int num_tokens, int nh, int nkv, int d, int dv, int D, OT* __restrict__ q,
-                     OT* __restrict__ k, OT* __restrict__ v, const PrepCommit c, int* status) {
-    extern __shared__ float prep_buf[];
+                     OT* __restrict__ k, OT* __restrict__ v, long long ldq, long long ldkv, const PrepCommit c,
+                     int* status) {
+    extern __shared__ __align__(16) float prep_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int dmax = d > dv ? d : dv;
-    float* buf = prep_buf + (size_t)warp * dmax;
-    const int hs_count = nh + 2 * nkv;
-    const long long row = (long long)blockIdx.x * PREP_WARPS + warp;
+    const int dmax = ((d > dv ? d : dv) + 3) & ~3;
+    const int half = rot / 2;
+    float* ang = prep_smem;                                    // cos[half], sin[half]
+    float* buf = prep_smem + ((rot + 3) & ~3) + (size_t)warp * dmax;
+    const int t = blockIdx.x;
     pdl_sync();
-    if (row >= (long long)num_tokens * hs_count) return;
-    const int t = (int)(row / hs_count), hs = (int)(row % hs_count);
-    const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
-    const int head = is_q ? hs : is_k ? hs - nh : hs - nh - nkv;
-    const int n = (is_q || is_k) ? d : dv;
-    const float* src = proj + (size_t)t * ld + (is_q ? (size_t)head * d
-                                                      : is_k ? (size_t)nh * d + (size_t)head * d
-                                                             : (size_t)(nh + nkv) * d + (size_t)head * dv);
     const int p_int = pos[t];
-    float ss = 0.f;
-    for (int e = lane; e < n; e += 32) {
-        const float x = src[e];
-        buf[e] = x;
-        ss += x * x;
-    }
-    const float* nw = is_q ? q_norm : is_k ? k_norm : nullptr;
-    if (nw) {
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-        for (int e = lane; e < n; e += 32) buf[e] = buf[e] * inv * nw[e];
-    }
-    __syncwarp();
-    if ((is_q || is_k) && rot > 0) {
-        const int half = rot / 2;
+    {
         const float p = (float)p_int;
-        for (int i = lane; i < half; i += 32) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
             float sn, cs;
             sincosf(p * freq[i], &sn, &cs);
-            cs *= mscale, sn *= mscale;
-            const float a = buf[i], b = buf[i + half];
-            buf[i] = rot_lo(a, b, cs, sn);
-            buf[i + half] = rot_hi(a, b, cs, sn);
+            ang[i] = cs * mscale, ang[half + i] = sn * mscale;
         }
-        __syncwarp();
     }
-    OT* dst = is_q ? q + ((size_t)t * nh + head) * D : (is_k ? k : v) + ((size_t)t * nkv + head) * D;
-    for (int e = lane; e < D; e += 32) st_f(dst + e, e < n ? buf[e] : 0.f);
-    if (!is_q && c.k_cache) {
+    __syncthreads();
+    // where the token's key and value go in the cache, if they are to be appended here
+    bool append = false;
+    CachePos cp;
+    cp.page = 0, cp.off = 0;
+    if (c.k_cache) {
         const int s = seq_of_token[t];
         if (s >= 0 && !(c.ring > 0 && p_int < c.seq_end[s] - c.ring)) {
-            const CachePos cp = cache_pos(p_int, c.ring, c.tables + (size_t)c.slots[s] * c.table_stride, c.page_size,
-                                          c.num_pages, status);
-            OT* cd = (OT*)(is_k ? c.k_cache : c.v_cache) + cache_index(cp, head, nkv, c.page_size, D);
-            for (int e = lane; e < D; e += 32) st_f(cd + e, e < n ? buf[e] : 0.f);
+            cp = cache_pos(p_int, c.ring, c.tables + (size_t)c.slots[s] * c.table_stride, c.page_size, c.num_pages,
+                           status);
+            append = true;
+        }
+    }
+    const int hs_count = nh + 2 * nkv;
+    const int hs = blockIdx.y * PREP_WARPS + warp;
+    if (hs < hs_count) {
+        const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
+        const int head = is_q ? hs : is_k ? hs - nh : hs - nh - nkv;
+        const int n = (is_q || is_k) ? d : dv;
+        const float* src = proj + (size_t)t * ld + (is_q ? (size_t)head * d
+                                                          : is_k ? (size_t)nh * d + (size_t)head * d
+                                                                 : (size_t)(nh + nkv) * d + (size_t)head * dv);
+        float ss = 0.f;
+        if (VEC) {
+            for (int e = lane * 4; e < n; e += 128) {
+                const float4 x = *reinterpret_cast<const float4*>(src + e);
+                *reinterpret_cast<float4*>(buf + e) = x;
+                ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+            }
+        } else {
+            for (int e = lane; e < n; e += 32) {
+                const float x = src[e];
+                buf[e] = x;
+                ss += x * x;
+            }
+        }
+        const float* nw = is_q ? q_norm : is_k ? k_norm : nullptr;
+        if (nw) {
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+            // (each lane scales the elements it loaded itself)
+            if (VEC) {
+                for (int e = lane * 4; e < n; e += 128) {
+                    float4 x = *reinterpret_cast<float4*>(buf + e);
+                    const float4 w = *reinterpret_cast<const float4*>(nw + e);
+                    x.x = x.x * inv * w.x, x.y = x.y * inv * w.y, x.z = x.z * inv * w.z, x.w = x.w * inv * w.w;
+                    *reinterpret_cast<float4*>(buf + e) = x;
+                }
+            } else {
+                for (int e = lane; e < n; e += 32) buf[e] = buf[e] * inv * nw[e];
+            }
+        }
+        __syncwarp();
+        if ((is_q || is_k) && rot > 0) {
+            for (int i = lane; i < half; i += 32) {
+                const float cs = ang[i], sn = ang[half + i];
+                const float a = buf[i], b = buf[i + half];
+                buf[i] = rot_lo(a, b, cs, sn);
+                buf[i + half] = rot_hi(a, b, cs, sn);
+            }
+            __syncwarp();
+        }
+        OT* dst = is_q ? q + (size_t)t * ldq + (size_t)head * D : (is_k ? k : v) + (size_t)t * ldkv + (size_t)head * D;
+        OT* cd = (!is_q && append) ? (OT*)(is_k ? c.k_cache : c.v_cache) + cache_index(cp, head, nkv, c.page_size, D)
+                                   : nullptr;
+        if (VEC) {
+            for (int e = lane * 4; e < D; e += 128) {
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e < n) x = *reinterpret_cast<const float4*>(buf + e);
+                prep_store4(dst + e, x.x, x.y, x.z, x.w);
+                if (cd) prep_store4(cd + e, x.x, x.y, x.z, x.w);
+            }
+        } else {
+            for (int e = lane; e < D; e += 32) {
+                const float x = e < n ? buf[e] : 0.f;
+                st_f(dst + e, x);
+                if (cd) st_f(cd + e, x);
+            }
         }
     }
 }
 
 // proj: [T, ld] 32-bit, bias added: q heads (nh * d), k heads (nkv * d), v heads (nkv * dv), then
-// whatever else the layer projected.  q: [T, nh, D]; k, v: [T, nkv, D].
+// whatever else the layer projected.  q: [T, nh, D] with a token pitch of ldq elements; k, v:
+// [T, nkv, D] with a token pitch of ldkv (so the three may be parts of one row [q | k | v]).
 MOE_API int moe_heads_prepare(const float* proj, int ld, const int* pos, const int* seq_of_token, const float* q_norm,
                               const float* k_norm, float eps, const float* freq, int rot, float mscale,
                               int num_tokens, int nh, int nkv, int d, int dv, int D, void* q, void* k, void* v,
-                              int out_dt, void* k_cache, void* v_cache, const int* seq_end, const int* slots,
+                              long long ldq, long long ldkv, int out_dt, void* k_cache, void* v_cache, const int* seq_end, const int* slots,
                               const int* tables, int table_stride, int ring, int page_size, int num_pages,
                               int* status, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (rot > 0 && !freq) || d <= 0 || dv <= 0 || D < d || D < dv || !q ||
-        !k || !v || ld < (nh + nkv) * d + nkv * dv)
+        !k || !v || ld < (nh + nkv) * d + nkv * dv || ldq < (long long)nh * D || ldkv < (long long)nkv * D)
         return (int)cudaErrorInvalidValue;
     if (k_cache && (!v_cache || !seq_end || !slots || !tables || !seq_of_token)) return (int)cudaErrorInvalidValue;
     PrepCommit c{k_cache, v_cache, seq_end, slots, tables, table_stride, ring, page_size, num_pages};
-    const long long rows = (long long)num_tokens * (nh + 2 * nkv);
-    const unsigned blocks = (unsigned)((rows + PREP_WARPS - 1) / PREP_WARPS);
-    const size_t smem = (size_t)PREP_WARPS * (d > dv ? d : dv) * sizeof(float);
+    const int dmax = ((d > dv ? d : dv) + 3) & ~3;
+    const size_t smem = ((size_t)((rot + 3) & ~3) + (size_t)PREP_WARPS * dmax) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    if (out_dt == DT_F32)
-        return launch_pdl(heads_prepare_kernel<float>, blocks, PREP_WARPS * 32, smem, stream, proj, ld, pos,
-                          seq_of_token, q_norm, k_norm, eps, freq, rot, mscale, num_tokens, nh, nkv, d, dv, D,
-                          (float*)q, (float*)k, (float*)v, c, status);
-    return launch_pdl(heads_prepare_kernel<__nv_bfloat16>, blocks, PREP_WARPS * 32, smem, stream, proj, ld, pos,
-                      seq_of_token, q_norm, k_norm, eps, freq, rot, mscale, num_tokens, nh, nkv, d, dv, D,
-                      (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, c, status);
+    const dim3 grid(num_tokens, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    const size_t esz = out_dt == DT_F32 ? 4 : 2;
+    auto al = [](const void* p, size_t a) { return ((uintptr_t)p % a) == 0; };
+    const bool vec = d % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 && ldq % 4 == 0 && ldkv % 4 == 0 &&
+                     al(proj, 16) && al(q_norm, 16) && al(k_norm, 16) && al(q, 4 * esz) && al(k, 4 * esz) &&
+                     al(v, 4 * esz) && al(k_cache, 4 * esz) && al(v_cache, 4 * esz);
+#define PREP(OT_, VEC_)                                                                                             \
+    return launch_pdl(heads_prepare_kernel<OT_, VEC_>, grid, PREP_WARPS * 32, smem, stream, proj, ld, pos,          \
+                      seq_of_token, q_norm, k_norm, eps, freq, rot, mscale, num_tokens, nh, nkv, d, dv, D, (OT_*)q, \
+                      (OT_*)k, (OT_*)v, ldq, ldkv, c, status)
+    if (out_dt == DT_F32) {
+        if (vec) PREP(float, true);
+        PREP(float, false);
+    }
+    if (vec) PREP(__nv_bfloat16, true);
+    PREP(__nv_bfloat16, false);
+#undef PREP
 }
 
-template <typename OT>
+__device__ __forceinline__ float4 prep_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 prep_load4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+__device__ __forceinline__ float sigmoid32(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// One thread per four consecutive columns of a head (VEC) or per element.
+template <typename OT, bool VEC>
 __global__ void gate_pack_kernel(const OT* __restrict__ ctx, const float* __restrict__ gate, int ld, long long total,
                                  int nh, int dv, int D, OT* __restrict__ out) {
     pdl_sync();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (VEC ? 4 : 1);
     if (i >= total) return;
     const int w = nh * dv;
     const long long t = i / w;
     const int c = (int)(i % w), h = c / dv, j = c % dv;
-    float x = ld_f(ctx + ((size_t)t * nh + h) * D + j);
-    if (gate) x *= 1.0f / (1.0f + expf(-gate[(size_t)t * ld + c]));
-    st_f(out + i, x);
+    if (VEC) {
+        float4 x = prep_load4(ctx + ((size_t)t * nh + h) * D + j);
+        if (gate) {
+            const float4 g = *reinterpret_cast<const float4*>(gate + (size_t)t * ld + c);
+            x.x *= sigmoid32(g.x), x.y *= sigmoid32(g.y), x.z *= sigmoid32(g.z), x.w *= sigmoid32(g.w);
+        }
+        prep_store4(out + i, x.x, x.y, x.z, x.w);
+    } else {
+        float x = ld_f(ctx + ((size_t)t * nh + h) * D + j);
+        if (gate) x *= sigmoid32(gate[(size_t)t * ld + c]);
+        st_f(out + i, x);
+    }
 }
 
 // ctx: [T, nh, D]; gate: first gate logit of token 0 (row pitch ld, 32-bit) or null; out: [T, nh * dv].
@@ -137,10 +225,19 @@ MOE_API int moe_gate_pack(const void* ctx, const float* gate, int ld, int num_to
     const long long total = (long long)num_tokens * nh * dv;
     if (total <= 0) return 0;
     if (D < dv) return (int)cudaErrorInvalidValue;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dt == DT_F32)
-        return launch_pdl(gate_pack_kernel<float>, blocks, 256, 0, stream, (const float*)ctx, gate, ld, total, nh, dv,
-                          D, (float*)out);
-    return launch_pdl(gate_pack_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)ctx, gate, ld,
-                      total, nh, dv, D, (__nv_bfloat16*)out);
+    const size_t esz = dt == DT_F32 ? 4 : 2;
+    const bool vec = dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 && ((uintptr_t)gate % 16) == 0 &&
+                     ((uintptr_t)ctx % (4 * esz)) == 0 && ((uintptr_t)out % (4 * esz)) == 0;
+    const long long threads = vec ? total / 4 : total;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+#define PACK(OT_, VEC_)                                                                                        \
+    return launch_pdl(gate_pack_kernel<OT_, VEC_>, blocks, 256, 0, stream, (const OT_*)ctx, gate, ld, total, nh, dv, \
+                      D, (OT_*)out)
+    if (dt == DT_F32) {
+        if (vec) PACK(float, true);
+        PACK(float, false);
+    }
+    if (vec) PACK(__nv_bfloat16, true);
+    PACK(__nv_bfloat16, false);
+#undef PACK
 }

@@ -34,7 +34,7 @@ def lib():
         sig = {
             "moe_embed": [P, I, P, P, I, I, I, P, P, P, P, F, P],
             "moe_dyt": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
-            "moe_heads_prepare": [P, I, P, P, P, P, F, P, I, F, I, I, I, I, I, I, P, P, P, I, P, P, P, P, P, I, I, I, I, P, P],
+            "moe_heads_prepare": [P, I, P, P, P, P, F, P, I, F, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P, P, P, P, I, I, I, I, P, P],
             "moe_gate_pack": [P, P, I, I, I, I, I, P, I, P],
             "moe_rmsnorm": [P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_rmsnorm_combine": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, F, I, P, P],
@@ -49,9 +49,9 @@ def lib():
             "moe_split3": [P, P, LL, I, P],
             "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
-            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
             "moe_attention_tiled": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
-            "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
             "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, I, P],
@@ -283,14 +283,17 @@ def heads_prepare(proj, pos, seq_of_token, *, nh, nkv, d, dv, width, q, k, v, q_
     """From a step's 32-bit projection rows [q heads | k heads | v heads | ...]: per-head RMS norm of
     queries and keys (``q_norm`` / ``k_norm`` weights of size d, or None), rotation of the first ``rot``
     dimensions with ``freq`` and cos/sin scaled by ``mscale``, split into q [T, nh, width] and k, v
-    [T, nkv, width], zero-filled beyond d (dv).  ``commit=(view, batch)`` also appends keys and values
-    to that cache layer."""
+    [T, nkv, width], zero-filled beyond d (dv); the three may be views into one buffer [T, nh + 2 nkv,
+    width] (a token pitch of their own).  ``commit=(view, batch)`` also appends keys and values to that
+    cache layer."""
     _chk(proj, "proj", torch.float32, 2), _chk(pos, "pos", torch.int32, 1)
     T = proj.shape[0]
     for t, n in ((q, nh), (k, nkv), (v, nkv)):
-        _chk(t, "q/k/v")
-        if t.numel() < T * n * width or t.dtype != q.dtype:
-            raise KernelError("heads_prepare: output size or dtype")
+        if (not t.is_cuda or t.dtype != q.dtype or tuple(t.shape) != (T, n, width) or t.stride(2) != 1
+                or t.stride(1) != width or t.stride(0) < n * width):
+            raise KernelError("heads_prepare: q, k, v must be [T, heads, width] with dense heads, of one dtype")
+    if k.stride(0) != v.stride(0):
+        raise KernelError("heads_prepare: keys and values must have the same token pitch")
     if proj.shape[1] < (nh + nkv) * d + nkv * dv:
         raise KernelError("heads_prepare: projection width")
     for wn in (q_norm, k_norm):
@@ -313,7 +316,7 @@ def heads_prepare(proj, pos, seq_of_token, *, nh, nkv, d, dv, width, q, k, v, q_
         ts, ring, ps, npg = g.table.stride(0), g.ring, g.page_size, g.num_pages
     _ok(lib().moe_heads_prepare(_p(proj), proj.stride(0), _p(pos), _p(seq_of_token), _p(q_norm), _p(k_norm), float(eps),
                                 _p(freq) if rot else None, int(rot), float(mscale), T, nh, nkv, d, dv, width, _p(q),
-                                _p(k), _p(v), _dt(q), _p(kc), _p(vc), _p(se), _p(sl), _p(tb), ts, ring, ps, npg,
+                                _p(k), _p(v), q.stride(0), k.stride(0), _dt(q), _p(kc), _p(vc), _p(se), _p(sl), _p(tb), ts, ring, ps, npg,
                                 _p(status), _stream()), "heads_prepare")
 
 
@@ -528,19 +531,38 @@ def _head_blocks(nh: int, nkv: int) -> int:
     return nkv * (1 if group == 1 else -(-group // 2))
 
 
-def attention_decode(q, view, batch, out, *, nh, window, scale, status):
+def _gate_args(out, T, nh, hd, gate, dv):
+    """(gate pointer, its row pitch, dv) of a merge that writes [T, nh * dv] instead of [T, nh * hd]."""
+    if not dv:
+        if gate is not None:
+            raise KernelError("attention: a gate needs the value width dv")
+        return None, 0, 0
+    if not 0 < dv <= hd or out.numel() < T * nh * dv:
+        raise KernelError("attention: dv or the packed output's size")
+    if gate is None:
+        return None, 0, int(dv)
+    if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (T, nh * dv):
+        raise KernelError("attention: gate shape, dtype or layout")
+    return gate.data_ptr(), gate.stride(0), int(dv)
+
+
+def attention_decode(q, view, batch, out, *, nh, window, scale, status, gate=None, dv=0):
     """Attention of one new token per sequence over the cache alone (its own key already
-    appended); split along the keys and merged."""
+    appended); split along the keys and merged.  With ``dv`` the merge writes [T, nh * dv], the
+    first dv columns of every head, times sigmoid(``gate``) (a float32 column slice [T, nh * dv])
+    if given."""
     g = view.group
     T = batch.num_tokens
     if q.dtype != g.dtype or out.dtype != q.dtype:
         raise KernelError("attention: dtypes of queries, cache and output must agree")
+    gp, gld, gdv = _gate_args(out, T, nh, g.head_dim, gate, dv)
     nsplit = decode_splits(q.device, T, _head_blocks(nh, g.num_kv_heads), getattr(batch, "max_end", 0))
     partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=q.device)
     _ok(lib().moe_attention_decode(_p(q), _p(view.k), _p(view.v), _p(out), _p(partial), _dt(q),
                                    _p(batch.seq_of_token), _p(batch.pos), _p(batch.slots), _p(g.table),
                                    g.table.stride(0), g.ring, g.page_size, g.num_pages, T, nh, g.num_kv_heads,
-                                   g.head_dim, int(window or 0), float(scale), nsplit, _p(status), _stream()),
+                                   g.head_dim, int(window or 0), float(scale), nsplit, gp, gld, gdv, _p(status),
+                                   _stream()),
         "attention_decode")
 
 
@@ -558,13 +580,15 @@ def _tickets(device, n: int) -> torch.Tensor:
     return t
 
 
-def attention_decode_fused(qkv, inv_freq, rot, view, batch, out, *, nh, window, scale, status) -> bool:
+def attention_decode_fused(qkv, inv_freq, rot, view, batch, out, *, nh, window, scale, status, gate=None, dv=0) -> bool:
     """One token per sequence, ONE launch: rotate the step's q/k/v rows, append key and value to
     the cache layer ``view``, attend over the cache split along the keys, merge.  False (nothing
-    launched) if the head size is not one the fast kernel takes."""
+    launched) if the head size is not one the fast kernel takes.  ``gate`` / ``dv``: as in
+    ``attention_decode``."""
     _chk(qkv, "qkv", torch.float32, 2)
     g = view.group
     T = batch.num_tokens
+    gp, gld, gdv = _gate_args(out, T, nh, g.head_dim, gate, dv)
     if qkv.shape[1] != (nh + 2 * g.num_kv_heads) * g.head_dim or out.dtype != g.dtype:
         raise KernelError("attention_decode_fused: shapes or dtypes do not fit the cache")
     if rot:
@@ -576,7 +600,7 @@ def attention_decode_fused(qkv, inv_freq, rot, view, batch, out, *, nh, window, 
                                             _p(out), _p(partial), _p(tickets), _dt(out), _p(batch.seq_of_token),
                                             _p(batch.pos), _p(batch.slots), _p(g.table), g.table.stride(0), g.ring,
                                             g.page_size, g.num_pages, T, nh, g.num_kv_heads, g.head_dim,
-                                            int(window or 0), float(scale), nsplit, _p(status), _stream())
+                                            int(window or 0), float(scale), nsplit, gp, gld, gdv, _p(status), _stream())
     if code == -1:
         return False
     _ok(code, "attention_decode_fused")

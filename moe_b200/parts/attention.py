@@ -25,6 +25,7 @@ kernel ``heads_prepare`` stands where the rotation-and-split kernel stands other
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -68,8 +69,9 @@ class GQAttention(Part):
         pos = dict(p.get("position") or {"kind": "none"})
         self.position = make_part("position", PartSpec(pos.pop("kind"), pos, spec.prefix))
         # the prepared path: a kernel of its own between projection and attention, records of width D
+        self.cos_sin_scale = float(getattr(self.position, "cos_sin_scale", lambda: 1.0)())
         self.prepared = bool(self.vd != self.hd or self.qk_norm or self.out_gate or self.hd % 16
-                             or self.position.cos_sin_scale() != 1.0)
+                             or self.cos_sin_scale != 1.0)
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if self.prepared:
@@ -151,6 +153,9 @@ class GQAttention(Part):
                       else self.position.attention_scale() / math.sqrt(self.hd))
         if self.prepared:
             self.width = record_width(self.hd, self.vd, rt.is_bf16)
+        # (MOE_B200_PREPARED_FUSED=0: single-token steps append in heads_prepare and attend with the split
+        # kernel and its merge, for comparisons)
+        self._fused_decode = os.environ.get("MOE_B200_PREPARED_FUSED", "1") != "0"
 
     def _forward_prepared(self, rt, h, batch, cache_view):
         """Projection (queries, keys, values and gate logits in one product) -> per-head norm,
@@ -159,6 +164,23 @@ class GQAttention(Part):
         T, D, nh, nkv = batch.num_tokens, self.width, self.nh, self.nkv
         proj = linear(rt, h.act, self.wqkv, bias=self.bqkv)
         table, rot = self.position.rotary_table()
+        g0 = (nh + nkv) * self.hd + nkv * self.vd
+        gate = proj[:, g0:g0 + nh * self.vd] if self.out_gate else None
+        prep = dict(nh=nh, nkv=nkv, d=self.hd, dv=self.vd, width=D, q_norm=self.q_norm_w, k_norm=self.k_norm_w,
+                    eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0, freq=table, rot=rot,
+                    mscale=self.cos_sin_scale, status=rt.status)
+        if batch.all_decode and self._fused_decode:
+            # one token a sequence: the prepared heads stay 32-bit in one row [q | k | v], and ONE more
+            # launch appends key and value, attends over the cache split along the keys, merges the
+            # splits, multiplies by the gate and packs the heads
+            row = torch.empty((T, nh + 2 * nkv, D), dtype=torch.float32, device=proj.device)
+            core.heads_prepare(proj, batch.pos, batch.seq_of_token, q=row[:, :nh], k=row[:, nh:nh + nkv],
+                               v=row[:, nh + nkv:], **prep)
+            packed = rt.empty((T, nh * self.vd))
+            if core.attention_decode_fused(row.view(T, -1), None, 0, cache_view, batch, packed, nh=nh, window=self.window,
+                                           scale=self.scale, status=rt.status, gate=gate, dv=self.vd):
+                return linear(rt, packed, self.wo)
+            self._fused_decode = False       # a head size the fused kernel does not take
         q = rt.empty((T, nh, D))
         k_new, v_new = rt.empty((T, nkv, D)), rt.empty((T, nkv, D))
         ctx = rt.empty((T, nh, D))
@@ -167,14 +189,14 @@ class GQAttention(Part):
         # a step of one token a sequence reads its own key from the cache; whole prompts read nothing
         # from it: both may append at once.  A step that goes on from the cache appends afterwards.
         early = batch.all_decode or batch.all_fresh
-        core.heads_prepare(proj, batch.pos, batch.seq_of_token, nh=nh, nkv=nkv, d=self.hd, dv=self.vd, width=D, q=q,
-                           k=k_new, v=v_new, q_norm=self.q_norm_w, k_norm=self.k_norm_w,
-                           eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0, freq=table, rot=rot,
-                           mscale=self.position.cos_sin_scale(), commit=(cache_view, batch) if early else None,
-                           status=rt.status)
+        core.heads_prepare(proj, batch.pos, batch.seq_of_token, q=q, k=k_new, v=v_new,
+                           commit=(cache_view, batch) if early else None, **prep)
         if batch.all_decode:
-            core.attention_decode(q, cache_view, batch, ctx, nh=nh, window=self.window, scale=self.scale,
-                                  status=rt.status)
+            # (the merge of the splits multiplies by the gate and packs the heads)
+            packed = rt.empty((T, nh * self.vd))
+            core.attention_decode(q, cache_view, batch, packed, nh=nh, window=self.window, scale=self.scale,
+                                  status=rt.status, gate=gate, dv=self.vd)
+            return linear(rt, packed, self.wo)
         else:
             done = False
             if rt.is_bf16:
@@ -194,9 +216,7 @@ class GQAttention(Part):
                 core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
         if self.out_gate or D != self.vd:
             packed = rt.empty((T, nh * self.vd))
-            g0 = (nh + nkv) * self.hd + nkv * self.vd
-            core.gate_pack(ctx, packed, nh=nh, dv=self.vd, width=D,
-                           gate=proj[:, g0:g0 + nh * self.vd] if self.out_gate else None)
+            core.gate_pack(ctx, packed, nh=nh, dv=self.vd, width=D, gate=gate)
         else:
             packed = ctx.view(T, nh * D)
         return linear(rt, packed, self.wo)
