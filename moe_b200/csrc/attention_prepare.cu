@@ -38,10 +38,11 @@ __device__ __forceinline__ void prep_store4(__nv_bfloat16* p, float a, float b, 
     *reinterpret_cast<uint2*>(p) = u;
 }
 
-// A block takes PREP_WARPS heads of one token (grid: tokens x groups of heads): the token's angles
-// once a block (cos and sin of pos * freq[i], times mscale) in shared memory, then a warp per head:
-// load (four elements a lane where the sizes allow, VEC), sum of squares over the warp, scale,
-// rotate through a per-warp buffer, store.
+// A block works on one token (grid.y == 1: many tokens, every warp takes heads in turn) or on
+// PREP_WARPS heads of one token (few tokens: a warp a head, so that a step of one sequence is not one
+// block).  The token's angles once a block (cos and sin of pos * freq[i], times mscale) in shared
+// memory, then per head: load (four elements a lane where the sizes allow, VEC), sum of squares
+// over the warp, scale, rotate through a per-warp buffer, store.
 template <typename OT, bool VEC>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restrict__ pos,
@@ -81,18 +82,33 @@ heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
         }
     }
     const int hs_count = nh + 2 * nkv;
-    const int hs = blockIdx.y * PREP_WARPS + warp;
-    if (hs < hs_count) {
+    const int step = gridDim.y * PREP_WARPS;
+    const float* row = proj + (size_t)t * ld;
+    // where head slot hs starts in the projection row
+    auto head_src = [&](int hs) {
+        return row + (hs < nh ? (size_t)hs * d
+                              : hs < nh + nkv ? (size_t)nh * d + (size_t)(hs - nh) * d
+                                              : (size_t)(nh + nkv) * d + (size_t)(hs - nh - nkv) * dv);
+    };
+    int hs = blockIdx.y * PREP_WARPS + warp;
+    // (VEC) the first four elements a lane of the NEXT head are asked for before this head is worked
+    // on, so that a warp has two loads in flight instead of one
+    float4 ahead = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (VEC && hs < hs_count && lane * 4 < (hs < nh + nkv ? d : dv))
+        ahead = *reinterpret_cast<const float4*>(head_src(hs) + lane * 4);
+    for (; hs < hs_count; hs += step) {
         const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
         const int head = is_q ? hs : is_k ? hs - nh : hs - nh - nkv;
         const int n = (is_q || is_k) ? d : dv;
-        const float* src = proj + (size_t)t * ld + (is_q ? (size_t)head * d
-                                                          : is_k ? (size_t)nh * d + (size_t)head * d
-                                                                 : (size_t)(nh + nkv) * d + (size_t)head * dv);
+        const float* src = head_src(hs);
         float ss = 0.f;
         if (VEC) {
+            const float4 first = ahead;
+            const int nx = hs + step;
+            if (nx < hs_count && lane * 4 < (nx < nh + nkv ? d : dv))
+                ahead = *reinterpret_cast<const float4*>(head_src(nx) + lane * 4);
             for (int e = lane * 4; e < n; e += 128) {
-                const float4 x = *reinterpret_cast<const float4*>(src + e);
+                const float4 x = e < 128 ? first : *reinterpret_cast<const float4*>(src + e);
                 *reinterpret_cast<float4*>(buf + e) = x;
                 ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
             }
@@ -146,6 +162,7 @@ heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
                 if (cd) st_f(cd + e, x);
             }
         }
+        __syncwarp();
     }
 }
 
@@ -167,7 +184,9 @@ MOE_API int moe_heads_prepare(const float* proj, int ld, const int* pos, const i
     const int dmax = ((d > dv ? d : dv) + 3) & ~3;
     const size_t smem = ((size_t)((rot + 3) & ~3) + (size_t)PREP_WARPS * dmax) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    const dim3 grid(num_tokens, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS);
+    // few tokens: a warp per head; from 128 tokens on the blocks fill the GPU anyway and a block per
+    // token forms the token's angles once
+    const dim3 grid(num_tokens, num_tokens >= 128 ? 1 : (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     const size_t esz = out_dt == DT_F32 ? 4 : 2;
     auto al = [](const void* p, size_t a) { return ((uintptr_t)p % a) == 0; };

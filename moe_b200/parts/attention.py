@@ -153,9 +153,11 @@ class GQAttention(Part):
                       else self.position.attention_scale() / math.sqrt(self.hd))
         if self.prepared:
             self.width = record_width(self.hd, self.vd, rt.is_bf16)
-        # (MOE_B200_PREPARED_FUSED=0: single-token steps append in heads_prepare and attend with the split
-        # kernel and its merge, for comparisons)
-        self._fused_decode = os.environ.get("MOE_B200_PREPARED_FUSED", "1") != "0"
+        # Single-token steps append in heads_prepare and attend with the split kernel, whose merge gates
+        # and packs (three launches).  MOE_B200_PREPARED_FUSED=1 takes the fused decode kernel instead
+        # (two launches); measured slower on a B200 at widths of 2,048 and 4,096 (0.61 against 0.55 ms a
+        # step at one sequence, 1.33 against 1.27 at 64), so it is off by default.
+        self._fused_decode = os.environ.get("MOE_B200_PREPARED_FUSED", "0") == "1"
 
     def _forward_prepared(self, rt, h, batch, cache_view):
         """Projection (queries, keys, values and gate logits in one product) -> per-head norm,

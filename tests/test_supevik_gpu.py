@@ -310,6 +310,26 @@ def test_a_batch_of_portions_that_go_on_from_different_places(root, dtype):
         assert helpers.max_rel_err(torch.cat(rows[i]), plain_of(d, reqs[i])) < G.tol(dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_both_forms_of_the_single_token_step(root, dtype):
+    """The fused decode kernel (append, attention, merge, gate and packing in one launch) and the
+    default three launches give the same logits."""
+    import moe_b200
+    from moe_b200.engine import Engine
+
+    d = U.model_folder(root, "loop3")
+    toks = U.tokens(U.CONFIGS["loop3"]["vocab"], 120, 9)
+    got = {}
+    for fused in (False, True):
+        model = moe_b200.load_model(d, dtype=dtype)
+        for b in model.blocks:
+            b.mixer._fused_decode = fused
+        got[fused] = helpers.replay_tail(Engine(model, max_tokens=512), {"r": toks}, tail=90)["r"]
+        assert all(b.mixer._fused_decode == fused for b in model.blocks)      # (the kernel took the head sizes)
+        assert helpers.max_rel_err(got[fused], plain_of(d, toks)) < G.tol(dtype)
+    assert helpers.max_rel_err(got[True], got[False]) < G.tol_cut(dtype)
+
+
 # ----------------------------------------------------------------------------- edges that random weights would hide
 def with_window(delta):
     def edit(cfg):
