@@ -91,6 +91,7 @@ heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
                                               : (size_t)(nh + nkv) * d + (size_t)(hs - nh - nkv) * dv);
     };
     int hs = blockIdx.y * PREP_WARPS + warp;
+    const bool in_regs = VEC && d <= 128 && dv <= 128 && D <= 128 && rot % 8 == 0;
     // (VEC) the first four elements a lane of the NEXT head are asked for before this head is worked
     // on, so that a warp has two loads in flight instead of one
     float4 ahead = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -102,11 +103,56 @@ heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
         const int n = (is_q || is_k) ? d : dv;
         const float* src = head_src(hs);
         float ss = 0.f;
+        float4 first = ahead;
         if (VEC) {
-            const float4 first = ahead;
             const int nx = hs + step;
             if (nx < hs_count && lane * 4 < (nx < nh + nkv ? d : dv))
                 ahead = *reinterpret_cast<const float4*>(head_src(nx) + lane * 4);
+        }
+        OT* dst = is_q ? q + (size_t)t * ldq + (size_t)head * D : (is_k ? k : v) + (size_t)t * ldkv + (size_t)head * D;
+        OT* cd = (!is_q && append) ? (OT*)(is_k ? c.k_cache : c.v_cache) + cache_index(cp, head, nkv, c.page_size, D)
+                                   : nullptr;
+        if (VEC && in_regs) {
+            // heads of up to 128 with a rotated width that is a multiple of 8: a lane keeps its four
+            // elements in registers throughout, and the rotation's partner (i <-> i + rot/2) is the
+            // lane rot/8 further on or back
+            const bool mine = lane * 4 < n;
+            float4 x = mine ? first : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float* nw = is_q ? q_norm : is_k ? k_norm : nullptr;
+            if (nw) {
+                ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+                const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+                if (mine) {
+                    const float4 w = *reinterpret_cast<const float4*>(nw + lane * 4);
+                    x.x = x.x * inv * w.x, x.y = x.y * inv * w.y, x.z = x.z * inv * w.z, x.w = x.w * inv * w.w;
+                }
+            }
+            if ((is_q || is_k) && rot > 0) {
+                const int hl = half / 4;                   // lanes that hold one half of the rotated part
+                const int from = lane < hl ? lane + hl : lane < 2 * hl ? lane - hl : lane;
+                float4 y;
+                y.x = __shfl_sync(0xffffffffu, x.x, from), y.y = __shfl_sync(0xffffffffu, x.y, from);
+                y.z = __shfl_sync(0xffffffffu, x.z, from), y.w = __shfl_sync(0xffffffffu, x.w, from);
+                if (lane < 2 * hl) {
+                    const int i0 = (lane < hl ? lane : lane - hl) * 4;
+                    const float4 cs = *reinterpret_cast<const float4*>(ang + i0);
+                    const float4 sn = *reinterpret_cast<const float4*>(ang + half + i0);
+                    if (lane < hl) {
+                        x.x = rot_lo(x.x, y.x, cs.x, sn.x), x.y = rot_lo(x.y, y.y, cs.y, sn.y);
+                        x.z = rot_lo(x.z, y.z, cs.z, sn.z), x.w = rot_lo(x.w, y.w, cs.w, sn.w);
+                    } else {
+                        x.x = rot_hi(y.x, x.x, cs.x, sn.x), x.y = rot_hi(y.y, x.y, cs.y, sn.y);
+                        x.z = rot_hi(y.z, x.z, cs.z, sn.z), x.w = rot_hi(y.w, x.w, cs.w, sn.w);
+                    }
+                }
+            }
+            if (lane * 4 < D) {
+                prep_store4(dst + lane * 4, x.x, x.y, x.z, x.w);
+                if (cd) prep_store4(cd + lane * 4, x.x, x.y, x.z, x.w);
+            }
+            continue;
+        }
+        if (VEC) {
             for (int e = lane * 4; e < n; e += 128) {
                 const float4 x = e < 128 ? first : *reinterpret_cast<const float4*>(src + e);
                 *reinterpret_cast<float4*>(buf + e) = x;
@@ -145,9 +191,6 @@ heads_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
             }
             __syncwarp();
         }
-        OT* dst = is_q ? q + (size_t)t * ldq + (size_t)head * D : (is_k ? k : v) + (size_t)t * ldkv + (size_t)head * D;
-        OT* cd = (!is_q && append) ? (OT*)(is_k ? c.k_cache : c.v_cache) + cache_index(cp, head, nkv, c.page_size, D)
-                                   : nullptr;
         if (VEC) {
             for (int e = lane * 4; e < D; e += 128) {
                 float4 x = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -108,16 +108,18 @@ def test_dynamic_tanh_kernel_with_and_without_the_sum_in_front(H, bf16):
 
 
 @pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("extra", [5, 8])      # a row pitch that allows 16-byte accesses, and one that does not
 @pytest.mark.parametrize("nh,nkv,d,dv,rot,scaling", [(3, 1, 24, 40, 8, U.YARN), (4, 2, 32, 16, 32, None), (2, 2, 16, 16, 0, None),
-                                                      (5, 5, 40, 8, 16, dict(U.YARN, factor=1.5))])
-def test_heads_prepare_norm_rotation_split_and_zero_fill(bf16, nh, nkv, d, dv, rot, scaling):
+                                                      (5, 5, 40, 8, 16, dict(U.YARN, factor=1.5)), (2, 1, 20, 20, 12, None),
+                                                      (9, 3, 128, 128, 64, U.YARN), (2, 1, 160, 96, 32, None)])
+def test_heads_prepare_norm_rotation_split_and_zero_fill(bf16, extra, nh, nkv, d, dv, rot, scaling):
     from moe_b200.config.spec import PartSpec
     from moe_b200.ops import core
     from moe_b200.parts.attention import record_width
     from moe_b200.parts.base import make_part
 
     g = torch.Generator().manual_seed(d * dv)
-    T, extra = 11, 5
+    T = 11
     width = (nh + nkv) * d + nkv * dv + extra
     proj = torch.randn(T, width, generator=g) * 3
     pos = torch.tensor([0, 1, 2, 63, 64, 65, 500, 1000, 4095, 7, 7], dtype=torch.int32)
@@ -325,7 +327,10 @@ def test_both_forms_of_the_single_token_step(root, dtype):
         for b in model.blocks:
             b.mixer._fused_decode = fused
         got[fused] = helpers.replay_tail(Engine(model, max_tokens=512), {"r": toks}, tail=90)["r"]
-        assert all(b.mixer._fused_decode == fused for b in model.blocks)      # (the kernel took the head sizes)
+        # (records of 64 ... 512 bytes: all of this model's in bfloat16; in float32 the layer with heads of
+        # 48 has records of 192 bytes, which the fused kernel declines, and goes back to three launches)
+        took = [b.mixer._fused_decode for b in model.blocks]
+        assert took == ([fused] * 4 if dtype == "bfloat16" else [fused, fused, False, fused])
         assert helpers.max_rel_err(got[fused], plain_of(d, toks)) < G.tol(dtype)
     assert helpers.max_rel_err(got[True], got[False]) < G.tol_cut(dtype)
 
