@@ -53,6 +53,12 @@ CONFIGS = {
     "sharp": dict(vocab=80, width=64, scale=4.0, eps=1e-5, loop=(0, 1, 2), layers=[
         layer(mixer(4, 2, 32, 32, window=9, rot=16, scaling=YARN, scale=1.5), ff=64),
         layer(mixer(4, 2, 32, 32, window=None, rot=32, scale=1.5), ff=64)]),
+    # sizes that are multiples of little: heads of 40 and 80 (records are filled up), a rotated width of
+    # 20 (not a multiple of 8), widths that no 16-byte access fits, four passes over a single layer
+    "odd": dict(vocab=203, width=72, scale=0.5, eps=1e-4, loop=(0, 1, 4), layers=[
+        layer(mixer(6, 3, 40, 24, window=100, rot=20, scaling=dict(YARN, factor=2.5, original=32)), ff=100),
+        layer(mixer(3, 1, 80, 96, window=33, rot=80, base=123.0), ff=52),
+        layer(mixer(5, 5, 18, 6, window=5, rot=6, scaling=dict(YARN, factor=16.0)), ff=None)]),
     # one layer that sees everything, without rotation: the tests make one far key stand out in it
     "far": dict(vocab=70, width=32, scale=3.0, eps=1e-5, loop=None, layers=[
         layer(mixer(2, 1, 16, 16, window=None, rot=0, scale=1.0), ff=48)]),

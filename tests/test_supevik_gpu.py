@@ -19,7 +19,7 @@ import supevik_util as U
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["loop3", "ones", "plain", "sharp"]
+NAMES = ["loop3", "odd", "ones", "plain", "sharp"]
 
 
 @pytest.fixture(scope="module")

@@ -106,7 +106,9 @@ def test_steps_without_wanted_logits_write_nothing(model_dirs, tmp_path):
 
 
 @pytest.mark.parametrize("bad,needle", [
-    ('{"step": 1, "entries": [{"id": "b", "tokens": [1] * 200, "want": []}]}'.replace("[1] * 200", str([1] * 200)), "CacheError"),
+    # (the cache has room for --max-tokens and for every request's last, partly filled page: 128 + 63 x 128)
+    pytest.param('{"step": 1, "entries": [{"id": "b", "tokens": [1] * 9000, "want": []}]}'.replace("[1] * 9000", str([1] * 9000)),
+                 "CacheError", id="more tokens than the cache holds"),
     ('{"entries": []}', "KeyError"),
     ('not a step', "JSONDecodeError"),
     ('{"step": 1, "entries": [{"id": "a", "tokens": [5], "want": [3]}]}', "wanted place"),
