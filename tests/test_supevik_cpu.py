@@ -84,7 +84,7 @@ def test_a_configuration_that_cannot_be_a_model_is_refused_in_words(edit, word):
 
 @pytest.mark.parametrize("rot", [
     {"dims": 16, "base": 10000.0, "scaling": U.YARN},
-    {"dims": 64, "base": 500000.0, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+    {"dims": 64, "base": 250000.0, "scaling": {"factor": 6.0, "original": 2048, "fast": 24.0, "slow": 1.5}},
     {"dims": 8, "base": 100.0, "scaling": {"factor": 1.5, "original": 64, "fast": 16.0, "slow": 2.0}},
     {"dims": 32, "base": 10000.0, "scaling": {"factor": 2.0, "original": 16, "fast": 1.0, "slow": 1.0}},   # lo == hi
 ])
@@ -105,8 +105,8 @@ def test_yarn_frequencies_and_factor(rot):
 def test_record_width():
     from moe_b200.parts.attention import record_width
 
-    assert record_width(96, 96, True) == 128 and record_width(32, 16, True) == 64 and record_width(64, 64, True) == 64
-    assert record_width(16, 160, True) == 160 and record_width(40, 24, False) == 48 and record_width(96, 96, False) == 96
+    assert record_width(80, 72, True) == 128 and record_width(32, 16, True) == 64 and record_width(64, 64, True) == 64
+    assert record_width(16, 160, True) == 160 and record_width(40, 24, False) == 48 and record_width(80, 72, False) == 80
 
 
 def test_the_plain_windowed_attention_sees_exactly_the_window():
