@@ -193,6 +193,8 @@ def step_bytes(model, live_lengths: List[int]) -> Tuple[float, float]:
     for e in model.spec.schedule:
         blk = model.blocks[e.layer]
         weights += sum(p.step_elements(B) for p in blk.parts())
+        if e.join is not None:
+            weights += model.joins[e.join].step_elements(B)
         req = blk.mixer.kv_request()
         if req is not None:
             per_pos = 2 * req.num_kv_heads * req.head_dim * esize

@@ -133,3 +133,20 @@ def test_info_prints_a_supevik_folder_in_the_words_of_its_parts(tmp_path, capsys
     assert "token embedding x 5" in out and "join with the embedding output" in out
     assert "Dynamic Tanh" in out and "sigmoid output gate" in out and "window 21" in out and "YaRN x4 from 64" in out
     assert "dense gated gelu_tanh 96   (2 of 3)" in out and "value heads of 16" in out
+
+
+def test_bytes_of_a_decode_step_count_every_layer_run_and_every_join(tmp_path):
+    import moe_b200
+    from moe_b200 import cli
+
+    d = U.model_folder(tmp_path, "loop3")
+    m = moe_b200.load_model(d, dtype="float32", device="cpu")
+    w = U.draw_weights(U.config_dict("loop3"), 11)
+    per_layer = [sum(t.numel() for n, t in w.items() if n.startswith(f"l{i}.")) for i in range(4)]
+    runs = [0, 1, 2, 1, 2, 1, 2, 3]
+    want = sum(per_layer[l] for l in runs) + 3 * w["loop.in"].numel() + w["head"].numel() + 2 * 64 + 1 + 2 * 64
+    got, kv = cli.step_bytes(m, [30, 30])
+    assert got == 4 * want
+    # windows of 7, 7, 21, 7 bound what the eight runs read: records of 32, 32, 48 and 32 floats for keys and for values
+    per_pos = {0: 2 * 2 * 32, 1: 2 * 1 * 32, 2: 2 * 2 * 48, 3: 2 * 2 * 32}
+    assert kv == 4 * 2 * sum(per_pos[l] * (21 if l == 2 else 7) for l in runs)
