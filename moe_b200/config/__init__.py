@@ -11,3 +11,4 @@ from .registry import (  # noqa: F401
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry  # noqa: F401
 from .qwen2_moe import Qwen2MoeConfig  # noqa: F401  (registers the architecture)
 from .supevik import SupevikConfig  # noqa: F401  (registers the architecture)
+from .fogapel import FogapelConfig  # noqa: F401  (registers the architecture)

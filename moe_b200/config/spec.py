@@ -37,6 +37,10 @@ class LayerSpec:
     # norms on the OUTPUT of the mixer and of the feed-forward, before the residual sum ("sandwich")
     post1: Optional[PartSpec] = None
     post2: Optional[PartSpec] = None
+    # per-channel factors on the mixer's and the feed-forward's output before the residual sum
+    # (parts of category "scale"; block "parallel")
+    scale1: Optional[PartSpec] = None
+    scale2: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -144,7 +144,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         float* __restrict__ partial, const int* __restrict__ seq_of_token,
                         const int* __restrict__ pos, const int* __restrict__ slots, const int* __restrict__ tables,
                         int table_stride, int ring, int page_size, int num_pages, int nh, int nkv, int window,
-                        float scale, int* status, const FusedArgs fa, int l2_prefetch_budget) {
+                        float scale, int* status, const FusedArgs fa, int l2_prefetch_budget, const AttnVariant av) {
     constexpr int EPC = Chunk<T>::N;       // elements per 16-byte chunk
     constexpr int HD = LPR * EPC;
     constexpr int RPI = 32 / LPR;          // rows per load instruction
@@ -170,7 +170,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     const int sub = lane % LPR, rgrp = lane / LPR;
     const int s = seq_of_token[t];
     const int p = s < 0 ? 0 : pos[t];
-    const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+    const int lo = attn_lo(p, window, av.chunk);
     // fused: position p is this step's own key, which comes from the q/k/v row, not from the cache
     const int hi = FUSED ? p - 1 : p;
     const int half = FUSED ? fa.rot / 2 : 0;
@@ -276,7 +276,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
             for (int g = 0; g < GH; g++) {
                 if (g >= gh) continue;                    // uniform
-                const float x = valid ? sc[g] * scale : -INFINITY;
+                const float x = valid ? attn_score(sc[g], scale, av.softcap) : -INFINITY;
                 const float m_new = fmaxf(m[g], warp_max(x));
                 float pr = 0.f, alpha = 1.f;
                 if (m_new != -INFINITY) {                 // uniform: at least one valid key so far
@@ -322,7 +322,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                 for (int e = 0; e < EPC; e++) d = fmaf(kn[e], qc[g][e], d);
 #pragma unroll
                 for (int off = LPR / 2; off >= 1; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-                const float x = d * scale;
+                const float x = attn_score(d, scale, av.softcap);
                 const float m_new = fmaxf(m[g], x);
                 const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
                 const float pr = expf(x - m_new);
@@ -401,7 +401,8 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
             ll += f * __ldcg(base + (size_t)sp * REC + HD + 1);
             a += f * __ldcg(base + (size_t)sp * REC + d);
         }
-        write_head_column((T*)fa.out, GateOut{fa.gate, fa.gate_ld, fa.dv}, t, nh, h, HD, d, a / ll);
+        write_head_column((T*)fa.out, GateOut{fa.gate, fa.gate_ld, fa.dv}, t, nh, h, HD, d,
+                          a / attn_denominator(mm, ll, av.sink));
     }
 }
 
@@ -413,7 +414,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         float* __restrict__ partial, const int* __restrict__ seq_of_token,
                         const int* __restrict__ pos, const int* __restrict__ slots,
                         const int* __restrict__ tables, int table_stride, int ring, int page_size, int num_pages,
-                        int nh, int nkv, int hd, int window, float scale, int* status) {
+                        int nh, int nkv, int hd, int window, float scale, int* status, const AttnVariant av) {
     extern __shared__ float sm[];
     pdl_sync();
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, t = blockIdx.z;
@@ -423,7 +424,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     const int s = seq_of_token[t];
     if (s < 0) return;
     const int p = pos[t];
-    const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+    const int lo = attn_lo(p, window, av.chunk);
     const int n_keys = p + 1 - lo;
     int per = (n_keys + nsplit - 1) / nsplit;
     per = (per + 31) & ~31;
@@ -480,7 +481,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
             for (int g = 0; g < GHS; g++) {
                 if (g < gh) {
-                    const float x = valid ? sc[g] * scale : -INFINITY;
+                    const float x = valid ? attn_score(sc[g], scale, av.softcap) : -INFINITY;
                     const float m_new = fmaxf(m[g], warp_max(x));
                     const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
                     pr[g] = valid ? expf(x - m_new) : 0.f;
@@ -546,7 +547,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          const int* __restrict__ seq_of_token, int nh, int hd, int nsplit,
-                                         const GateOut go) {
+                                         const GateOut go, int sink) {
     pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const int rec = hd + 2;
@@ -569,7 +570,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* _
             const float ms = base[(size_t)s * rec + hd];
             if (ms != -INFINITY) a += expf(ms - mm) * base[(size_t)s * rec + d];
         }
-        write_head_column(out, go, t, nh, h, hd, d, a / ll);
+        write_head_column(out, go, t, nh, h, hd, d, a / attn_denominator(mm, ll, sink));
     }
 }
 
@@ -591,7 +592,8 @@ template <typename T>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
            const int* seq_of_token, const int* pos, const int* slots, const int* tables, int table_stride, int ring,
            int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
-           int* status, cudaStream_t stream, const FusedArgs* fused = nullptr, const GateOut go = GateOut{nullptr, 0, 0}) {
+           int* status, cudaStream_t stream, const FusedArgs* fused = nullptr, const GateOut go = GateOut{nullptr, 0, 0},
+           const AttnVariant av = AttnVariant{0, 0.f, 0}) {
     const int group = nh / nkv;
     dim3 grid(nsplit, nkv, num_tokens);
     const int row_bytes = hd * (int)sizeof(T);
@@ -611,11 +613,11 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
         if (fused)                                                                                                \
             rc = launch_pdl(attn_decode_fast_kernel<T, LPR, GH, true>, grid, WARPS * 32, 0, stream, (const T*)q,  \
                             (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables,      \
-                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa, budget); \
+                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa, budget, av); \
         else                                                                                                      \
             rc = launch_pdl(attn_decode_fast_kernel<T, LPR, GH, false>, grid, WARPS * 32, 0, stream, (const T*)q, \
                             (const T*)k_cache, (const T*)v_cache, partial, seq_of_token, pos, slots, tables,      \
-                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa, budget); \
+                            table_stride, ring, page_size, num_pages, nh, nkv, window, scale, status, fa, budget, av); \
     } while (0)
 #define FAST_G(LPR)                  \
     do {                             \
@@ -636,13 +638,13 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
         const size_t smem = ((size_t)GHS * hd + (size_t)WARPS * GHS * (hd + 2)) * sizeof(float);
         rc = launch_pdl(attn_decode_rows_kernel<T>, grid, WARPS * 32, smem, stream, (const T*)q, (const T*)k_cache,
                         (const T*)v_cache, partial, seq_of_token, pos, slots, tables, table_stride, ring, page_size,
-                        num_pages, nh, nkv, hd, window, scale, status);
+                        num_pages, nh, nkv, hd, window, scale, status, av);
     }
 #undef FAST
 #undef FAST_G
     if (fused || rc) return rc;
     return launch_pdl(attn_decode_merge_kernel<T>, dim3(num_tokens, nh), 128, 0, stream, (const float*)partial, (T*)out,
-                      seq_of_token, nh, hd, nsplit, go);
+                      seq_of_token, nh, hd, nsplit, go, av.sink);
 }
 
 }  // namespace
@@ -685,10 +687,12 @@ MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void*
                                  int dt, const int* seq_of_token, const int* pos, const int* slots,
                                  const int* tables, int table_stride, int ring, int page_size, int num_pages,
                                  int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
-                                 const float* gate, int gate_ld, int dv, int* status, cudaStream_t stream) {
+                                 const float* gate, int gate_ld, int dv, int* status, int chunk, float softcap,
+                                 int sink, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (dv < 0 || dv > hd || (gate && dv == 0)) return (int)cudaErrorInvalidValue;
     const GateOut go{gate, gate_ld, dv};
+    const AttnVariant av{chunk, softcap, sink};
     if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh <= 0 || nh > 65535 || nh % nkv != 0 || nsplit < 1 ||
         nsplit > 65535 || nkv > 65535 || num_tokens > 65535 || !q || !k_cache || !v_cache || !out || !partial)
         return (int)cudaErrorInvalidValue;
@@ -698,10 +702,10 @@ MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void*
     if (dt == DT_F32)
         return launch<float>(q, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride, ring,
                              page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status, stream,
-                             nullptr, go);
+                             nullptr, go, av);
     return launch<__nv_bfloat16>(q, k_cache, v_cache, out, partial, seq_of_token, pos, slots, tables, table_stride,
                                  ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale, nsplit, status,
-                                 stream, nullptr, go);
+                                 stream, nullptr, go, av);
 }
 
 // ---- the entry point that allocates nothing (see attention_decode_noalloc.h) -----------------

@@ -1,7 +1,8 @@
 // Attention of this step's queries over the cache: the plain kernel.
 //
 // For the query at position p of a sequence (reference: src/model.rs:794-827):
-//   lo = window ? max(0, p + 1 - window) : 0
+//   lo = window ? max(0, p + 1 - window) : 0   (or the start of p's chunk; see AttnVariant in
+//   common.cuh for this and for the capped score and the softmax with a sink)
 //   s_j = (q . k_j) * scale for j in [lo, p];  softmax (subtract max, exp, divide
 //   by the sum);  o = sum_j s_j v_j;  kv head = head / (heads / kv_heads).
 // Scores, the softmax and the weighted sum are 32-bit whatever the storage type.
@@ -54,7 +55,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const 
                     const int* __restrict__ seq_start, const int* __restrict__ cu_seqlens,
                     const int* __restrict__ slots, const int* __restrict__ tables, int table_stride, int ring,
                     int page_size, int num_pages, int nh, int nkv, int hd, int window, float scale, int use_local,
-                    int* status) {
+                    int* status, const AttnVariant av) {
     __shared__ __align__(16) float qs[MAX_HD];
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int s = seq_of_token[t];
@@ -65,7 +66,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const 
     }
     const int p = pos[t];
     const int p0 = use_local ? seq_start[s] : p + 1;
-    const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+    const int lo = attn_lo(p, window, av.chunk);
     const int kvh = h / (nh / nkv);
     const int tok0 = cu_seqlens[s];
     const int* table = tables + (size_t)slots[s] * table_stride;
@@ -92,7 +93,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const 
                 kp = k_cache + r, vp = v_cache + r;
             }
         }
-        const float sc = valid ? dot_row(kp, qs, hd) * scale : -INFINITY;
+        const float sc = valid ? attn_score(dot_row(kp, qs, hd), scale, av.softcap) : -INFINITY;
         const float m_new = fmaxf(m, warp_max(sc));
         const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
         const float pr = valid ? expf(sc - m_new) : 0.f;
@@ -111,7 +112,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const 
             }
         }
     }
-    const float inv = 1.0f / l;
+    const float inv = 1.0f / attn_denominator(m, l, av.sink);
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; i++) {
         const int d = lane + 32 * i;
@@ -126,7 +127,8 @@ MOE_API int moe_attention_generic(const void* q, const void* k_new, const void* 
                                   const int* seq_start, const int* cu_seqlens, const int* slots, const int* tables,
                                   int table_stride, int ring, int page_size, int num_pages, int num_tokens, int nh,
                                   int nkv, int hd, int window, float scale, int use_local, int* status,
-                                  cudaStream_t stream) {
+                                  int chunk, float softcap, int sink, cudaStream_t stream) {
+    const AttnVariant av{chunk, softcap, sink};
     if (num_tokens <= 0) return 0;
     if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535)
         return (int)cudaErrorInvalidValue;
@@ -135,12 +137,12 @@ MOE_API int moe_attention_generic(const void* q, const void* k_new, const void* 
         attn_generic_kernel<float><<<grid, 32, 0, stream>>>(
             (const float*)q, (const float*)k_new, (const float*)v_new, (const float*)k_cache, (const float*)v_cache,
             (float*)out, seq_of_token, pos, seq_start, cu_seqlens, slots, tables, table_stride, ring, page_size,
-            num_pages, nh, nkv, hd, window, scale, use_local, status);
+            num_pages, nh, nkv, hd, window, scale, use_local, status, av);
     else
         attn_generic_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new,
             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, seq_of_token, pos,
             seq_start, cu_seqlens, slots, tables, table_stride, ring, page_size, num_pages, nh, nkv, hd, window,
-            scale, use_local, status);
+            scale, use_local, status, av);
     return launch_status();
 }

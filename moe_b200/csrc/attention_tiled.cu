@@ -45,7 +45,7 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
                   const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
                   const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start, const int* __restrict__ slots,
                   const int* __restrict__ tables, int table_stride, int ring, int num_pages, int num_seqs, int nh,
-                  int nkv, int hd, int window, float scale, int use_local, int* status) {
+                  int nkv, int hd, int window, float scale, int use_local, int* status, const AttnVariant var) {
     extern __shared__ __align__(16) float sm[];
     __shared__ int s_seq, s_tile;
     float* Qt = sm;                               // [hd][BQ + PAD]
@@ -78,7 +78,7 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
     const int rows = min(BQ, cnt - r0);
     const int p_first = start + r0, p_last = p_first + rows - 1;   // positions of the tile's queries
     const int local_from = use_local ? start : p_last + 1;         // positions from here on come from k_new / v_new
-    const int lo_min = window > 0 ? max(0, p_first + 1 - window) : 0;
+    const int lo_min = attn_lo(p_first, window, var.chunk);   // (the first query's: lo never decreases with p)
     const int* table = tables + (size_t)slots[seq] * table_stride;
     const int QS = BQ + PAD, KS = BK + PAD, VS = hd + PAD, PS = BK + PAD;
 
@@ -145,13 +145,13 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int row = ty * 4 + r, p = p_first + row;
-            const int lo = window > 0 ? max(0, p + 1 - window) : 0;
+            const int lo = attn_lo(p, window, var.chunk);
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 const int j = j0 + tx * 4 + c;
                 const bool seen = row < rows && j <= p && j >= lo;
-                s[r][c] = seen ? s[r][c] * scale : -INFINITY;
+                s[r][c] = seen ? attn_score(s[r][c], scale, var.softcap) : -INFINITY;
                 mx = fmaxf(mx, s[r][c]);
             }
 #pragma unroll
@@ -207,7 +207,7 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
     for (int r = 0; r < 4; r++) {
         const int row = ty * 4 + r;
         if (row >= rows) continue;
-        const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+        const float inv = l[r] > 0.f ? 1.0f / attn_denominator(m[r], l[r], var.sink) : 0.f;
         T* dst = out + ((size_t)(tok0 + r0 + row) * nh + h) * hd;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -234,8 +234,10 @@ MOE_API int moe_attention_tiled(const void* q, const void* k_new, const void* v_
                                 const void* v_cache, void* out, int dt, const int* cu_seqlens, const int* seq_start,
                                 const int* slots, const int* tables, int table_stride, int ring, int page_size,
                                 int num_pages, int num_seqs, int num_tokens, int nh, int nkv, int hd, int window,
-                                float scale, int use_local, int* status, cudaStream_t stream) {
+                                float scale, int use_local, int* status, int chunk, float softcap, int sink,
+                                cudaStream_t stream) {
     if (num_tokens <= 0 || num_seqs <= 0) return 0;
+    const AttnVariant av{chunk, softcap, sink};
     if (hd % 16 != 0 || hd > 256 || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
     if (page_size != BK || (ring % BK) != 0) return -1;
     const size_t align = dt == DT_F32 ? 16 : 8;          // rows are read four elements at a time
@@ -255,7 +257,7 @@ MOE_API int moe_attention_tiled(const void* q, const void* k_new, const void* v_
         attn_tiled_kernel<TT><<<grid, THREADS, smem, stream>>>(                                                       \
             (const TT*)q, (const TT*)k_new, (const TT*)v_new, (const TT*)k_cache, (const TT*)v_cache, (TT*)out,       \
             cu_seqlens, seq_start, slots, tables, table_stride, ring, num_pages, num_seqs, nh, nkv, hd, window, scale, \
-            use_local, status);                                                                                       \
+            use_local, status, av);                                                                                   \
     } while (0)
     if (dt == DT_F32)
         GO(float);

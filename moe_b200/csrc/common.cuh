@@ -77,12 +77,41 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return t;
 }
 
-// The gate's activation of a gated feed-forward, act(g) * u.
-enum : int { ACT_SILU = 0, ACT_GELU_TANH = 1 };
-__device__ __forceinline__ float glu_mul(int act, float g, float u) {
+// The gate's activation of a gated feed-forward, act(g) * u.  ACT_CLAMPED_SIGMOID has a constant
+// `param` (the limit L): g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1).
+enum : int { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_CLAMPED_SIGMOID = 2 };
+__device__ __forceinline__ float glu_mul(int act, float param, float g, float u) {
     if (act == ACT_GELU_TANH)      // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
         return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    if (act == ACT_CLAMPED_SIGMOID) {
+        g = fminf(g, param);
+        u = fminf(fmaxf(u, -param), param);
+        return (g / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+    }
     return (g / (1.0f + expf(-g))) * u;
+}
+
+// ---- variants of the attention score and mask, shared by every attention kernel ----------------
+//   chunk > 0   position p sees the keys of its own chunk only: lo = (p / chunk) * chunk (chunks are
+//               counted from position 0 of the sequence); else window > 0: lo = max(0, p + 1 - window)
+//   softcap > 0 the scaled score s becomes softcap * tanh(s / softcap)
+//   sink        the softmax has one more term of score 0 that carries no value: the denominator
+//               is 1 + sum_j exp(s_j)
+struct AttnVariant {
+    int chunk;
+    float softcap;
+    int sink;
+};
+__device__ __forceinline__ int attn_lo(int p, int window, int chunk) {
+    return chunk > 0 ? (p / chunk) * chunk : (window > 0 ? max(0, p + 1 - window) : 0);
+}
+__device__ __forceinline__ float attn_score(float dot, float scale, float softcap) {
+    const float s = dot * scale;
+    return softcap > 0.f ? softcap * tanhf(s / softcap) : s;
+}
+// the denominator of a softmax whose running maximum is m and running sum (relative to m) is l
+__device__ __forceinline__ float attn_denominator(float m, float l, int sink) {
+    return sink ? l + expf(-m) : l;
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }

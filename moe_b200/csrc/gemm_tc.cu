@@ -67,7 +67,8 @@ struct Params {
     int* status;
     uint32_t wait_limit;        // microseconds a wait on a barrier may take (WAIT_LIMIT_US, less in the wait test)
     int test_fault;             // 0; the wait test: 1 = the producer loads nothing, 2 = no MMA is issued
-    int act;                    // SWIGLU: the gate's activation (ACT_SILU, ACT_GELU_TANH)
+    int act;                    // SWIGLU: the gate's activation (ACT_* in common.cuh)
+    float act_param;            // its constant, if it has one (the limit of ACT_CLAMPED_SIGMOID)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -473,7 +474,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     for (int j = 0; j < 16; j++) {
                         const int t = row0 + c0 + j;
                         if (n_ok && t < row_end) {
-                            const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, a[j], b[j]) : a[j] + bias;
+                            const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], b[j]) : a[j] + bias;
                             if (p.out_bf16)
                                 ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
                             else
@@ -540,7 +541,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                     sa += va[r][s];
                                     if (MODE == MODE_SWIGLU) sb += vb[r][s];
                                 }
-                                const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, sa, sb) : sa + bias;
+                                const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, sa, sb) : sa + bias;
                                 if (p.out_bf16)
                                     ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
                                 else
@@ -591,7 +592,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         sa += va[r][s];
                         if (MODE == MODE_SWIGLU) sb += vb[r][s];
                     }
-                    const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, sa, sb) : sa + bias;
+                    const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, sa, sb) : sa + bias;
                     if (p.out_bf16)
                         ((__nv_bfloat16*)p.out)[(size_t)(row0 + t) * p.ldo + n] = __float2bfloat16_rn(v);
                     else
@@ -630,13 +631,13 @@ __device__ __forceinline__ void epilogue_part(const Params& p, uint32_t taddr, i
 #pragma unroll
             for (int j = 0; j < 32; j++)
                 if (n_ok && row0 + c0 + j < row_end)
-                    o[(size_t)j * p.ldo] = __float2bfloat16_rn(MODE == MODE_SWIGLU ? glu_mul(p.act, a[j], bb[j]) : a[j] + bias);
+                    o[(size_t)j * p.ldo] = __float2bfloat16_rn(MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], bb[j]) : a[j] + bias);
         } else {
             float* o = (float*)p.out + (size_t)(row0 + c0) * p.ldo + n;
 #pragma unroll
             for (int j = 0; j < 32; j++)
                 if (n_ok && row0 + c0 + j < row_end)
-                    o[(size_t)j * p.ldo] = MODE == MODE_SWIGLU ? glu_mul(p.act, a[j], bb[j]) : a[j] + bias;
+                    o[(size_t)j * p.ldo] = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], bb[j]) : a[j] + bias;
         }
     }
 }
@@ -656,7 +657,7 @@ __device__ __forceinline__ void epilogue_part_il(const Params& p, uint32_t taddr
         for (int j = 0; j < 32; j += 2) {
             const float send = upper ? a[j] : a[j + 1];
             const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
-            const float v = upper ? glu_mul(p.act, recv, a[j + 1]) : glu_mul(p.act, a[j], recv);
+            const float v = upper ? glu_mul(p.act, p.act_param, recv, a[j + 1]) : glu_mul(p.act, p.act_param, a[j], recv);
             const int r = row0 + c0 + j + (upper ? 1 : 0);
             if (n_ok && r < row_end) {
                 if (p.out_bf16)
@@ -1207,7 +1208,8 @@ int launch_pair(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p,
 // Returns 0, a CUDA error code, or -1 if the shape cannot be handled (the caller falls back).
 MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, int N, int K, int mode, void* out,
                         int out_bf16, int ldo, const float* bias, const int* group_offsets, int M, int bn, int splits,
-                        float* partials, int* tickets, int* status, int early_offsets, int act, cudaStream_t stream) {
+                        float* partials, int* tickets, int* status, int early_offsets, int act, float act_param,
+                        cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -1;
     const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
@@ -1225,7 +1227,7 @@ MOE_API int moe_gemm_tc(const void* X, int ldx, const void* W, int num_groups, i
     p.out = out, p.out_bf16 = out_bf16, p.ldo = ldo, p.bias = bias, p.group_offsets = group_offsets;
     p.num_groups = num_groups, p.M = M, p.N = N, p.K = K, p.w_rows_per_group = w_rows, p.splits = splits;
     p.kb_per_split = per, p.partials = partials, p.tickets = tickets, p.status = status;
-    p.wait_limit = g_wait_limit, p.test_fault = g_test_fault, p.act = act;
+    p.wait_limit = g_wait_limit, p.test_fault = g_test_fault, p.act = act, p.act_param = act_param;
     // token tiles: sum over groups of ceil(rows / bn) <= (non-empty groups) + floor(M / bn); CTAs past
     // the real count leave at once, but each still reserves its shared memory, so the bound is kept tight
     if (splits == 1 && bn >= 128 && g_persistent && (!group_offsets || num_groups <= MAX_SMEM_GROUPS)) {

@@ -230,7 +230,8 @@ __global__ void sum_slices_kernel(const float* __restrict__ part, float* __restr
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, float* sc, int lane, bool padding,
                                             int num_experts, int rows, int top_k, int norm_topk, float scale,
                                             int* __restrict__ idx_out, float* __restrict__ w_out,
-                                            float* __restrict__ gate_out, float* wk = nullptr) {
+                                            float* __restrict__ gate_out, float* wk = nullptr,
+                                            const float* __restrict__ bias = nullptr) {
     // wk: top_k floats of shared memory for the picked weights before scaling (else they are
     // staged in w_out itself, which costs round trips to global memory)
     if (!wk) wk = w_out;
@@ -240,12 +241,13 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
         return;
     }
     if (gate_out && rows > num_experts && lane == 0) *gate_out = 1.0f / (1.0f + expf(-lg[num_experts]));
+    // (bias: one constant per expert, added to its logit before anything else looks at it)
     float m = -INFINITY;
-    for (int e = lane; e < num_experts; e += 32) m = fmaxf(m, lg[e]);
+    for (int e = lane; e < num_experts; e += 32) m = fmaxf(m, lg[e] + (bias ? bias[e] : 0.f));
     m = warp_max(m);
     float z = 0.f;
     for (int e = lane; e < num_experts; e += 32) {
-        const float v = expf(lg[e] - m);
+        const float v = expf(lg[e] + (bias ? bias[e] : 0.f) - m);
         sc[e] = v;
         z += v;
     }
@@ -299,7 +301,7 @@ __global__ void __launch_bounds__(128)
 router_topk_kernel(float* __restrict__ logits, const float* __restrict__ part, int slices,
                    const int* __restrict__ seq_of_token, int num_tokens, int num_experts, int rows, int top_k,
                    int norm_topk, float scale, int* __restrict__ topk_idx, float* __restrict__ topk_w,
-                   float* __restrict__ shared_gate) {
+                   float* __restrict__ shared_gate, const float* __restrict__ bias) {
     extern __shared__ float sc_all[];   // per warp: rows logits, num_experts scores, top_k weights
     pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -321,7 +323,7 @@ router_topk_kernel(float* __restrict__ logits, const float* __restrict__ part, i
     __syncwarp();
     route_token(lg, lg + rows, lane, seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
                 topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr,
-                lg + rows + num_experts);
+                lg + rows + num_experts, bias);
 }
 
 // Inverting the (token, expert) table, by one block.  pairs = tokens * top_k entries of topk_idx
@@ -381,14 +383,15 @@ route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ 
                       int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
                       float* __restrict__ topk_w, float* __restrict__ shared_gate, int* __restrict__ offsets,
                       int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, const uint4* __restrict__ x,
-                      uint4* __restrict__ xs, int row_units, int* status) {
+                      uint4* __restrict__ xs, int row_units, int* status, const float* __restrict__ bias) {
     extern __shared__ float dyn[];   // 32 warps x num_experts floats, then counts[E], cursor[E]
     pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = warp; t < num_tokens; t += 32)
         route_token(logits + (size_t)t * rows, dyn + (size_t)warp * num_experts, lane,
                     seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
-                    topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr);
+                    topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr,
+                    nullptr, bias);
     __syncthreads();   // the picks were written by this block: visible to it after the barrier
     int* counts = reinterpret_cast<int*>(dyn + (size_t)32 * num_experts);
     const int pairs = num_tokens * top_k;
@@ -407,13 +410,14 @@ route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ 
 // act[m, j] = f(gu[m, j]) * gu[m, inter + j], f = silu, silu(a) = a / (1 + exp(-a))
 // (reference: src/model.rs:31-33), or another gate activation (glu_mul in common.cuh).
 template <typename OT>
-__global__ void swiglu_kernel(const float* __restrict__ gu, OT* __restrict__ act, long long total, int inter, int f) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, OT* __restrict__ act, long long total, int inter, int f,
+                              float f_param) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long m = i / inter;
     const int j = (int)(i % inter);
     const float a = gu[m * 2 * inter + j], b = gu[m * 2 * inter + inter + j];
-    st_f(act + i, glu_mul(f, a, b));
+    st_f(act + i, glu_mul(f, f_param, a, b));
 }
 
 // One block per token: out[t] = sum_j w[t, j] * y[pos_of_pair[t k + j]] + g[t] * shared[t]
@@ -874,7 +878,7 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
 MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
                        int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
                        float* logits, int* topk_idx, float* topk_w, float* shared_gate, float* scratch,
-                       long long scratch_floats, cudaStream_t stream) {
+                       long long scratch_floats, const float* bias, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
     if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
@@ -891,13 +895,13 @@ MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt
     }
     return launch_pdl(router_topk_kernel, (num_tokens + 3) / 4, 128, smem, stream, logits,
                       (const float*)(slices ? scratch : nullptr), slices, seq_of_token, num_tokens, num_experts, rows,
-                      top_k, norm_topk, scale, topk_idx, topk_w, shared_gate);
+                      top_k, norm_topk, scale, topk_idx, topk_w, shared_gate, bias);
 }
 
 // Picks, weights and shared gate from logits that are already there ([T, rows] float32).
 MOE_API int moe_router_topk(float* logits, const int* seq_of_token, int num_tokens, int num_experts, int has_gate_row,
                             int top_k, int norm_topk, float scale, int* topk_idx, float* topk_w, float* shared_gate,
-                            cudaStream_t stream) {
+                            const float* bias, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits || (has_gate_row && !shared_gate))
         return (int)cudaErrorInvalidValue;
@@ -909,7 +913,8 @@ MOE_API int moe_router_topk(float* logits, const int* seq_of_token, int num_toke
         if (e != cudaSuccess) return (int)e;
     }
     return launch_pdl(router_topk_kernel, (num_tokens + 3) / 4, 128, smem, stream, logits, (const float*)nullptr, 0,
-                      seq_of_token, num_tokens, num_experts, rows, top_k, norm_topk, scale, topk_idx, topk_w, shared_gate);
+                      seq_of_token, num_tokens, num_experts, rows, top_k, norm_topk, scale, topk_idx, topk_w, shared_gate,
+                      bias);
 }
 
 // A float32 row as three bfloat16 terms, x = p0 + p1 + p2 exactly (8 + 8 + 8 bits of mantissa):
@@ -959,24 +964,25 @@ MOE_API int moe_align(const int* topk_idx, int num_tokens, int top_k, int num_ex
 MOE_API int moe_route_dispatch(const float* logits, const int* seq_of_token, int num_tokens, int num_experts,
                                int has_gate_row, int top_k, int norm_topk, float scale, int* topk_idx, float* topk_w,
                                float* shared_gate, int* offsets, int* sorted_token, int* pos_of_pair, const void* x,
-                               void* xs, int row_bytes, int* status, cudaStream_t stream) {
+                               void* xs, int row_bytes, int* status, const float* bias, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (num_tokens > 64 || num_experts > 256 || top_k <= 0 || top_k > num_experts || row_bytes % 16)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)32 * num_experts * sizeof(float) + (size_t)2 * num_experts * sizeof(int);
     return launch_pdl(route_dispatch_kernel, 1, 1024, smem, stream, logits, seq_of_token, num_tokens, num_experts,
                       num_experts + (has_gate_row ? 1 : 0), top_k, norm_topk, scale, topk_idx, topk_w, shared_gate,
-                      offsets, sorted_token, pos_of_pair, (const uint4*)x, (uint4*)xs, row_bytes / 16, status);
+                      offsets, sorted_token, pos_of_pair, (const uint4*)x, (uint4*)xs, row_bytes / 16, status, bias);
 }
 
-MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, int inter, int f, cudaStream_t stream) {
+MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, int inter, int f, float f_param,
+                       cudaStream_t stream) {
     const long long total = rows * inter;
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dt == DT_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gu, (float*)act, total, inter, f);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gu, (float*)act, total, inter, f, f_param);
     else
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)act, total, inter, f);
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)act, total, inter, f, f_param);
     return launch_status();
 }
 

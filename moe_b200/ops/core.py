@@ -16,7 +16,7 @@ from . import build
 
 DT_F32, DT_BF16 = 0, 1
 # the gate's activation of a gated feed-forward (ACT_* in csrc/common.cuh)
-GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2}
 
 
 class KernelError(RuntimeError):
@@ -42,19 +42,27 @@ def lib():
             "moe_gemm_generic": [P, I, I, P, I, P, I, LL, P, I, I, P, P, I, I, I, I, P, P],
             "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, P, P],
             "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
-            "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
-            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P],
+            "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, F, I, P],
+            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P, P],
             "moe_router_logits": [P, P, P, I, I, I, I, P, P, LL, P],
-            "moe_router_topk": [P, P, I, I, I, I, I, F, P, P, P, P],
+            "moe_router_topk": [P, P, I, I, I, I, I, F, P, P, P, P, P],
             "moe_split3": [P, P, LL, I, P],
-            "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P],
+            "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
-            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
-            "moe_attention_tiled": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, I, F, I, P],
+            "moe_attention_tiled": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, I, F, I, P],
+            "moe_conv_heads_prepare": [P, I, P, I, P, LL, P, P, P, P, F, I, P, I, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P,
+                                       P, P, I, I, I, I, P, P],
+            "moe_conv_state_update": [P, I, P, LL, I, I, P, P, I, P],
+            "moe_wkv_shift_mix": [P, P, I, P, LL, P, P, P, P, I, I, P, I, P, P],
+            "moe_wkv_decay": [P, P, P, I, I, I, P, P],
+            "moe_wkv_scan": [P, P, P, P, LL, P, P, LL, P, P, I, I, I, P, P],
+            "moe_wkv_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
+            "moe_rmsnorm_scaled": [P, P, P, P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
             "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
-            "moe_swiglu": [P, P, I, LL, I, I, P],
+            "moe_swiglu": [P, P, I, LL, I, I, F, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
             "moe_sample": [P, I, I, P, P, P, I, F, I, F, F, P, P, P, LL, I, P],
             "moe_logprobs": [P, I, I, P, I, P, P, P, P],
@@ -335,6 +343,142 @@ def gate_pack(ctx, out, *, nh, dv, width, gate=None):
     _ok(lib().moe_gate_pack(_p(ctx), _p(gate), ld, T, nh, dv, width, _p(out), _dt(out), _stream()), "gate_pack")
 
 
+def conv_heads_prepare(proj, batch, *, nh, nkv, d, dv, width, q, k, v, taps_w=None, state=None, eps=0.0,
+                       unit_norm=False, freq=None, rot=0, commit=None, status=None):
+    """From a step's 32-bit projection rows [q heads | k heads | v heads]: a causal convolution over
+    time on every channel (``taps_w`` float32 [channels, taps]; earlier rows come from the step or,
+    before it, from ``state`` [slots + 1, >= (taps - 1) * channels]; None: no convolution), the
+    rotation of pairs (2i, 2i + 1) of the first ``rot`` dimensions of query and key heads, their
+    division by the head's root mean square (``unit_norm``), and the split into q [T, nh, width] and
+    k, v [T, nkv, width], zero-filled.  ``commit=view`` also appends keys and values to that cache
+    layer.  The state is not changed: ``conv_state_update`` does that afterwards."""
+    _chk(proj, "proj", torch.float32, 2)
+    T = proj.shape[0]
+    channels = (nh + nkv) * d + nkv * dv
+    for t, n in ((q, nh), (k, nkv), (v, nkv)):
+        if (not t.is_cuda or t.dtype != q.dtype or tuple(t.shape) != (T, n, width) or t.stride(2) != 1
+                or t.stride(1) != width or t.stride(0) < n * width):
+            raise KernelError("conv_heads_prepare: q, k, v must be [T, heads, width] with dense heads, of one dtype")
+    if k.stride(0) != v.stride(0) or proj.shape[1] < channels:
+        raise KernelError("conv_heads_prepare: token pitch of keys and values, or projection width")
+    taps = 1
+    if taps_w is not None:
+        _chk(taps_w, "taps", torch.float32, 2)
+        taps = taps_w.shape[1]
+        if taps_w.shape[0] != channels:
+            raise KernelError("conv_heads_prepare: one row of taps per channel")
+        if taps > 1:
+            _chk(state, "state", torch.float32, 2)
+    if rot:
+        _chk(freq, "freq", torch.float32, 1)
+        if freq.numel() < rot // 2:
+            raise KernelError("conv_heads_prepare: frequency table too short")
+    kc = vc = se = tb = None
+    ts = ring = ps = npg = 0
+    if commit is not None:
+        g = commit.group
+        if k.dtype != g.dtype or g.num_kv_heads != nkv or g.head_dim != width:
+            raise KernelError("conv_heads_prepare: the cache layer differs from the keys in dtype or shape")
+        kc, vc, se, tb = commit.k, commit.v, batch.seq_end, g.table
+        ts, ring, ps, npg = g.table.stride(0), g.ring, g.page_size, g.num_pages
+    _ok(lib().moe_conv_heads_prepare(_p(proj), proj.stride(0), _p(taps_w), taps, _p(state),
+                                     state.stride(0) if state is not None else 0, _p(batch.pos), _p(batch.seq_of_token),
+                                     _p(batch.cu_seqlens), _p(batch.slots), float(eps), 1 if unit_norm else 0,
+                                     _p(freq) if rot else None, int(rot), T, nh, nkv, d, dv, width, _p(q), _p(k), _p(v),
+                                     q.stride(0), k.stride(0), _dt(q), _p(kc), _p(vc), _p(se), _p(tb), ts, ring, ps, npg,
+                                     _p(status), _stream()), "conv_heads_prepare")
+
+
+def conv_state_update(proj, state, batch, *, taps, channels):
+    """state[slot] <- the last ``taps - 1`` rows of ``proj`` that each sequence of the step holds by now."""
+    _chk(proj, "proj", torch.float32, 2), _chk(state, "state", torch.float32, 2)
+    _ok(lib().moe_conv_state_update(_p(proj), proj.stride(0), _p(state), state.stride(0), int(taps), int(channels),
+                                    _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs, _stream()), "conv_state_update")
+
+
+def wkv_shift_mix(h32, mu, state, batch, out, last32=None):
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]; the row before a step's first is ``state[slot,
+    :width]`` (zeros at position 0), which afterwards holds the sequence's last row of the step.
+    ``last32`` (float32 [T, width]) receives the last blend instead of ``out``."""
+    _chk(h32, "h", torch.float32, 2), _chk(mu, "mu", torch.float32, 2), _chk(state, "state", torch.float32, 2)
+    T, W = h32.shape
+    _chk(out, "out", dims=3)
+    if mu.shape[1] != W or out.shape[1:] != (T, W) or out.shape[0] < mu.shape[0] - (1 if last32 is not None else 0) \
+            or state.shape[1] < W:
+        raise KernelError("wkv_shift_mix: shapes")
+    if last32 is not None:
+        _chk(last32, "last32", torch.float32, 2)
+        if tuple(last32.shape) != (T, W):
+            raise KernelError("wkv_shift_mix: shapes")
+    _ok(lib().moe_wkv_shift_mix(_p(h32), _p(mu), mu.shape[0], _p(state), state.stride(0), _p(batch.seq_of_token),
+                                _p(batch.pos), _p(batch.cu_seqlens), _p(batch.slots), T, W, _p(out), _dt(out), _p(last32),
+                                _stream()),
+        "wkv_shift_mix")
+
+
+def wkv_decay(low, w2, w0, out):
+    """out[t, i] = exp(-exp(w0[i] + sum_q w2[i, q] tanh(low[t, q]))): float32 throughout."""
+    _chk(low, "low", torch.float32, 2), _chk(w2, "w2", torch.float32, 2), _chk(w0, "w0", torch.float32, 1)
+    _chk(out, "out", torch.float32, 2)
+    T, R = low.shape
+    inner = w2.shape[0]
+    if w2.shape[1] != R or w0.numel() != inner or tuple(out.shape) != (T, inner):
+        raise KernelError("wkv_decay: shapes")
+    _ok(lib().moe_wkv_decay(_p(low), _p(w2), _p(w0), T, inner, R, _p(out), _stream()), "wkv_decay")
+
+
+def wkv_scan(r, k, v, w, u, state, batch, out, *, heads, d):
+    """Per sequence and head, tokens in order: o_t = (S + diag(u) k_t v_t^T)^T r_t, then
+    S <- diag(w_t) S + k_t v_t^T.  r, k, v, w: float32 [T, heads * d] of one row pitch
+    (column slices of one buffer are fine); ``state``: float32 [slots + 1, >= heads * d * d], S of every
+    slot; out: float32 [T, heads * d]."""
+    T = out.shape[0]
+    for t in (r, k, v, w):
+        if (not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or tuple(t.shape) != (T, heads * d)
+                or t.stride(1) != 1 or t.stride(0) != r.stride(0)):
+            raise KernelError("wkv_scan: r, k, v and the decay must be float32 [T, heads * d] of one row pitch")
+    _chk(u, "u", torch.float32), _chk(out, "out", torch.float32, 2)
+    if u.numel() != heads * d or state.dtype != torch.float32 or state.stride(1) != 1:
+        raise KernelError("wkv_scan: constants or state")
+    _ok(lib().moe_wkv_scan(_p(r), _p(k), _p(v), _p(w), r.stride(0), _p(u), _p(state), state.stride(0),
+                           _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs, heads, d, _p(out), _stream()), "wkv_scan")
+
+
+def wkv_finish(o, gate, norm_w, eps, batch, out, *, heads, d):
+    """out = o / rms(o over each head) * norm_w * silu(gate), rounded to ``out``'s dtype."""
+    _chk(o, "o", torch.float32, 2), _chk(norm_w, "norm weight", torch.float32, 1), _chk(out, "out", dims=2)
+    T = o.shape[0]
+    if gate.dtype != torch.float32 or gate.stride(1) != 1 or tuple(gate.shape) != (T, heads * d) or out.shape != o.shape:
+        raise KernelError("wkv_finish: shapes")
+    _ok(lib().moe_wkv_finish(_p(o), _p(gate), gate.stride(0), _p(norm_w), float(eps), _p(batch.seq_of_token), T, heads, d,
+                             _p(out), _dt(out), _stream()), "wkv_finish")
+
+
+def rmsnorm_scaled(x, a, sa, b, sb, weight, eps, *, rows=None, out32=None, out16=None, write_back=True, status=None):
+    """y = rmsnorm(x[r] + a[r] * sa + b[r] * sb) with per-channel scales sa, sb (``b``, ``sb`` may be
+    None); with ``write_back`` (and no ``rows``) the sum is stored back into ``x``."""
+    _chk(x, "x", torch.float32, 2), _chk(weight, "weight", torch.float32, 1)
+    _chk(a, "a", torch.float32, 2), _chk(sa, "sa", torch.float32, 1)
+    S, H = x.shape
+    n_out = S if rows is None else rows.numel()
+    if a.shape != x.shape or sa.numel() != H or weight.numel() != H:
+        raise KernelError("rmsnorm_scaled: shapes")
+    if b is not None:
+        _chk(b, "b", torch.float32, 2), _chk(sb, "sb", torch.float32, 1)
+        if b.shape != x.shape or sb.numel() != H:
+            raise KernelError("rmsnorm_scaled: shapes")
+    if rows is not None:
+        _chk(rows, "rows", torch.int32, 1)
+    for o, dt in ((out32, torch.float32), (out16, torch.bfloat16)):
+        if o is not None:
+            _chk(o, "out", dt, 2)
+            if o.shape[0] < n_out or o.shape[1] != H:
+                raise KernelError("rmsnorm_scaled: output shape")
+    _ok(lib().moe_rmsnorm_scaled(_p(x), _p(a), _p(sa), _p(b), _p(sb), _p(weight), _p(rows), _p(out32), _p(out16), n_out,
+                                 S, H, float(eps), 1 if (write_back and rows is None) else 0, _p(status), _stream()),
+        "rmsnorm_scaled")
+
+
 def add_inplace(a, b):
     _chk(a, "a", torch.float32), _chk(b, "b", torch.float32)
     if a.numel() != b.numel():
@@ -427,7 +571,16 @@ def kv_commit(k_new, v_new, view, batch, status):
         "kv_commit")
 
 
-def attention_generic(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status):
+def _variant(chunk, softcap, sink):
+    """(chunk, softcap, sink) as the kernels take them: see AttnVariant in csrc/common.cuh."""
+    return int(chunk or 0), float(softcap or 0.0), 1 if sink else 0
+
+
+def attention_generic(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status, chunk=0,
+                      softcap=0.0, sink=False):
+    """``chunk``: a position sees the keys of its own chunk of that many positions only (instead of a
+    window); ``softcap``: scores pass cap * tanh(s / cap); ``sink``: the softmax's denominator has one
+    more term exp(0).  The same three options in every attention kernel."""
     g = view.group
     T = batch.num_tokens
     if q.dtype != g.dtype or out.dtype != q.dtype:
@@ -436,10 +589,12 @@ def attention_generic(q, k_new, v_new, view, batch, out, *, nh, window, scale, u
                                     _p(batch.seq_of_token), _p(batch.pos), _p(batch.seq_start), _p(batch.cu_seqlens),
                                     _p(batch.slots), _p(g.table), g.table.stride(0), g.ring, g.page_size,
                                     g.num_pages, T, nh, g.num_kv_heads, g.head_dim, int(window or 0), float(scale),
-                                    1 if use_local else 0, _p(status), _stream()), "attention_generic")
+                                    1 if use_local else 0, _p(status), *_variant(chunk, softcap, sink), _stream()),
+        "attention_generic")
 
 
-def attention_tiled(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status) -> bool:
+def attention_tiled(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status, chunk=0, softcap=0.0,
+                    sink=False) -> bool:
     """The same as ``attention_generic`` with 64 queries of a (sequence, head) to a block and the
     keys staged through shared memory (32-bit arithmetic on the CUDA cores).  False, with nothing
     launched, for a layout it does not take (a page size other than 64, unaligned rows)."""
@@ -450,15 +605,24 @@ def attention_tiled(q, k_new, v_new, view, batch, out, *, nh, window, scale, use
                                      _p(batch.cu_seqlens), _p(batch.seq_start), _p(batch.slots), _p(g.table),
                                      g.table.stride(0), g.ring, g.page_size, g.num_pages, batch.num_seqs,
                                      batch.num_tokens, nh, g.num_kv_heads, g.head_dim, int(window or 0), float(scale),
-                                     1 if use_local else 0, _p(status), _stream())
+                                     1 if use_local else 0, _p(status), *_variant(chunk, softcap, sink), _stream())
     if code == -1:
         return False
     _ok(code, "attention_tiled")
     return True
 
 
+def _router_bias(bias, E):
+    if bias is not None:
+        _chk(bias, "router bias", torch.float32, 1)
+        if bias.numel() != E:
+            raise KernelError("router: one bias per expert")
+    return bias
+
+
 def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_gate_w=None, shared_gate=None,
-           seq_of_token=None):
+           seq_of_token=None, bias=None):
+    """``bias``: float32 [E], added to the logits before the softmax and the pick."""
     _chk(h32, "h", torch.float32, 2), _chk(w_router, "router weight", dims=2)
     T, H = h32.shape
     E = w_router.shape[0]
@@ -477,7 +641,7 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
     scratch = torch.empty((need,), dtype=torch.float32, device=h32.device) if need else None
     _ok(lib().moe_router(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), _p(seq_of_token), T, H, E, top_k,
                          1 if norm_topk else 0, float(scale), _p(logits), _p(topk_idx), _p(topk_w), _p(shared_gate),
-                         _p(scratch), need, _stream()), "router")
+                         _p(scratch), need, _p(_router_bias(bias, E)), _stream()), "router")
 
 
 def split3(x32: torch.Tensor) -> torch.Tensor:
@@ -489,7 +653,8 @@ def split3(x32: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def router_topk(logits, top_k, norm_topk, scale, topk_idx, topk_w, *, num_experts, shared_gate=None, seq_of_token=None):
+def router_topk(logits, top_k, norm_topk, scale, topk_idx, topk_w, *, num_experts, shared_gate=None, seq_of_token=None,
+                bias=None):
     """Picks and weights from logits [T, E (+ 1 row for the shared gate)] that are already there."""
     _chk(logits, "logits", torch.float32, 2)
     T = logits.shape[0]
@@ -497,7 +662,8 @@ def router_topk(logits, top_k, norm_topk, scale, topk_idx, topk_w, *, num_expert
     if logits.shape[1] not in (num_experts, num_experts + 1) or (gate_row and shared_gate is None):
         raise KernelError("router_topk: logits must have one column per expert (and one for the shared gate)")
     _ok(lib().moe_router_topk(_p(logits), _p(seq_of_token), T, num_experts, 1 if gate_row else 0, top_k,
-                              1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(shared_gate), _stream()),
+                              1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(shared_gate),
+                              _p(_router_bias(bias, num_experts)), _stream()),
         "router_topk")
 
 
@@ -546,7 +712,8 @@ def _gate_args(out, T, nh, hd, gate, dv):
     return gate.data_ptr(), gate.stride(0), int(dv)
 
 
-def attention_decode(q, view, batch, out, *, nh, window, scale, status, gate=None, dv=0):
+def attention_decode(q, view, batch, out, *, nh, window, scale, status, gate=None, dv=0, chunk=0, softcap=0.0,
+                     sink=False):
     """Attention of one new token per sequence over the cache alone (its own key already
     appended); split along the keys and merged.  With ``dv`` the merge writes [T, nh * dv], the
     first dv columns of every head, times sigmoid(``gate``) (a float32 column slice [T, nh * dv])
@@ -562,7 +729,7 @@ def attention_decode(q, view, batch, out, *, nh, window, scale, status, gate=Non
                                    _p(batch.seq_of_token), _p(batch.pos), _p(batch.slots), _p(g.table),
                                    g.table.stride(0), g.ring, g.page_size, g.num_pages, T, nh, g.num_kv_heads,
                                    g.head_dim, int(window or 0), float(scale), nsplit, gp, gld, gdv, _p(status),
-                                   _stream()),
+                                   *_variant(chunk, softcap, sink), _stream()),
         "attention_decode")
 
 
@@ -616,13 +783,14 @@ def moe_align(topk_idx, num_tokens, top_k, num_experts, offsets, sorted_token, p
                         _p(status), _stream()), "moe_align")
 
 
-def swiglu(gu, act, fn="silu"):
-    """act = fn(gu[:, :I]) * gu[:, I:]; ``fn`` is one of ``GLU_ACTS``."""
+def swiglu(gu, act, fn="silu", param=0.0):
+    """act = fn(gu[:, :I]) * gu[:, I:]; ``fn`` is one of ``GLU_ACTS``, ``param`` its constant if it has
+    one (the limit of "clamped_sigmoid": min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1))."""
     _chk(gu, "gu", torch.float32, 2), _chk(act, "act", dims=2)
     rows, two_i = gu.shape
     if two_i % 2 or act.shape != (rows, two_i // 2):
         raise KernelError("swiglu: shapes")
-    _ok(lib().moe_swiglu(_p(gu), _p(act), _dt(act), rows, two_i // 2, GLU_ACTS[fn], _stream()), "swiglu")
+    _ok(lib().moe_swiglu(_p(gu), _p(act), _dt(act), rows, two_i // 2, GLU_ACTS[fn], float(param), _stream()), "swiglu")
 
 
 def moe_combine(y, pos_of_pair, topk_w, top_k, out, *, shared=None, shared_gate=None):
@@ -742,7 +910,7 @@ def norm_route(x, delta, norm_w, eps, w_router, top_k, norm_topk, scale, *, bf16
 
 
 def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None, seq_of_token=None, gather=None,
-                   status=None):
+                   status=None, bias=None):
     """Few tokens (<= 64) and <= 256 experts: router logits, then pick + table inversion + gather in
     ONE more launch.  Returns (topk_idx, topk_w, shared_gate, offsets, sorted_token, pos_of_pair,
     gathered) where ``gathered[p] = gather[sorted_token[p]]`` (or None)."""
@@ -772,5 +940,5 @@ def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None
     _ok(lib().moe_route_dispatch(_p(logits), _p(seq_of_token), T, E, 1 if shared_gate_w is not None else 0, top_k,
                                  1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(sg), _p(offsets),
                                  _p(sorted_token), _p(pos_of_pair), _p(gather), _p(xs), row_bytes, _p(status),
-                                 _stream()), "route_dispatch")
+                                 _p(_router_bias(bias, E)), _stream()), "route_dispatch")
     return topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs

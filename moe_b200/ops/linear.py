@@ -31,19 +31,20 @@ def linear(rt, a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor]
     return out
 
 
-def swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+def swiglu_linear(rt, a: torch.Tensor, w_gate_up: torch.Tensor, act: str = "silu", act_param: float = 0.0) -> torch.Tensor:
     """act(a Wg^T) * (a Wu^T) with w_gate_up = [Wg; Wu] of shape [2 I, K]; returns [M, I] in the
-    compute dtype.  ``act``: the gate's activation, "silu" or "gelu_tanh"."""
+    compute dtype.  ``act``: the gated pair's function, one of ``core.GLU_ACTS`` (``act_param``: its
+    constant, if it has one)."""
     M, inter = a.shape[0], w_gate_up.shape[0] // 2
     out = torch.empty((M, inter), dtype=rt.compute_dtype, device=a.device)
     if _use_tc(rt, a, w_gate_up):
         from . import tc
 
-        if tc.gemm_tc(a, w_gate_up, out, swiglu=True, status=rt.status, act=act):
+        if tc.gemm_tc(a, w_gate_up, out, swiglu=True, status=rt.status, act=act, act_param=act_param):
             return out
     gu = torch.empty((M, 2 * inter), dtype=torch.float32, device=a.device)
     core.gemm_generic(a, w_gate_up, gu, status=rt.status)
-    core.swiglu(gu, out, act)
+    core.swiglu(gu, out, act, act_param)
     return out
 
 

@@ -23,7 +23,9 @@ def lib():
     if _lib is None:
         L = build.load("tc")
         P, I = c_void_p, c_int
-        L.moe_gemm_tc.argtypes = [P, I, P, I, I, I, I, P, I, I, P, P, I, I, I, P, P, P, I, I, P]
+        from ctypes import c_float as _F
+
+        L.moe_gemm_tc.argtypes = [P, I, P, I, I, I, I, P, I, I, P, P, I, I, I, P, P, P, I, I, _F, P]
         L.moe_gemm_tc.restype = c_int
         L.moe_gemm_tc_plan.argtypes = [I, I, I, I, I, I, P]
         L.moe_gemm_tc_plan.restype = c_int
@@ -126,9 +128,9 @@ def token_tile(rows_per_group: float, grouped: bool = False) -> int:
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool = False,
             bias: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
             bn: Optional[int] = None, splits: Optional[int] = None, status=None, early_offsets: bool = False,
-            act: str = "silu") -> bool:
+            act: str = "silu", act_param: float = 0.0) -> bool:
     """out = x @ w[g].T (PLAIN) or act(x @ gate.T) * (x @ up.T) (SwiGLU, w rows = gate then up; ``act``
-    is the gate's activation, one of ``core.GLU_ACTS``).
+    is the gate's activation, one of ``core.GLU_ACTS``, ``act_param`` its constant if it has one).
 
     x: [M, K] bf16 (row pitch a multiple of 8); w: [N', K] or [G, N', K] bf16 contiguous;
     out: [M, N] float32 or bfloat16 with N = N' (PLAIN) or N' / 2 (SwiGLU).
@@ -186,7 +188,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
                          None if partials is None else partials.data_ptr(),
                          None if tickets is None else tickets.data_ptr(),
                          None if status is None else status.data_ptr(), 1 if early_offsets else 0, core.GLU_ACTS[act],
-                         core._stream())
+                         float(act_param), core._stream())
     if code == -1:
         return False
     core._ok(code, "gemm_tc")

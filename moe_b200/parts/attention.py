@@ -21,6 +21,22 @@ kernel ``heads_prepare`` stands where the rotation-and-split kernel stands other
   out_gate    the concatenated heads are multiplied by sigmoid(Wg n), n being the same input as
               the other projections'; Wg is one more block of rows of the fused projection.
   a position encoding whose cos and sin carry a factor (``cos_sin_scale``).
+
+Options of the score and the mask, which every attention kernel of the 32-bit arithmetic takes
+(``AttnVariant`` in csrc/common.cuh):
+  chunk       position i sees j <= i with i // chunk == j // chunk, counted from the sequence's
+              first position (instead of a window); the cache keeps a ring of one chunk.
+  softcap     the scaled score s becomes cap * tanh(s / cap).
+  sink        the softmax's denominator is 1 + sum_j exp(s_j): a term of score 0 without a value.
+  o_bias      the output projection has a bias.
+
+A second prepared path, whose kernel ``conv_heads_prepare`` stands in the same place, is taken by
+  conv        {"taps": n}: a causal convolution over time on every channel of q, k and v right
+              after the projection, y_t = sum_j w[:, j] u_(t - n + 1 + j) (tensors [channels, n]);
+              the last n - 1 projected rows of a sequence are its state of fixed size;
+  unit_norm   {"eps": e}: after the rotation, query and key heads are divided by their root mean
+              square (no weight);
+  a rotation of pairs (2i, 2i + 1) (position option ``interleaved``).
 """
 from __future__ import annotations
 
@@ -50,7 +66,9 @@ class GQAttention(Part):
     graph_safe = True
     default_names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-                     "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "gate_proj.weight"}
+                     "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "gate_proj.weight",
+                     "o_bias": "o_proj.bias", "q_conv": "q_conv.weight", "k_conv": "k_conv.weight",
+                     "v_conv": "v_conv.weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -66,20 +84,41 @@ class GQAttention(Part):
         self.qk_norm = p.get("qk_norm")
         self.out_gate = bool(p.get("out_gate", False))
         self.fixed_scale = p.get("scale")
+        self.chunk = int(p.get("chunk") or 0)
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.sink = bool(p.get("sink", False))
+        self.o_bias = bool(p.get("o_bias", False))
+        self.taps = int((p.get("conv") or {}).get("taps", 0) or 0)
+        self.unit_norm = p.get("unit_norm")
         pos = dict(p.get("position") or {"kind": "none"})
         self.position = make_part("position", PartSpec(pos.pop("kind"), pos, spec.prefix))
         # the prepared path: a kernel of its own between projection and attention, records of width D
         self.cos_sin_scale = float(getattr(self.position, "cos_sin_scale", lambda: 1.0)())
         self.prepared = bool(self.vd != self.hd or self.qk_norm or self.out_gate or self.hd % 16
                              or self.cos_sin_scale != 1.0)
+        self.conv_path = bool(self.taps or self.unit_norm or getattr(self.position, "interleaved", False))
+        self.variant = dict(chunk=self.chunk, softcap=self.softcap, sink=self.sink)
+        self.plain_scores = not (self.chunk or self.softcap or self.sink)    # what the tensor-core kernels compute
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if self.chunk < 0 or self.softcap < 0 or self.taps < 0 or self.taps > 16:
+            raise ValueError("chunk and softcap must not be negative; a convolution has 1 to 16 taps")
+        if self.chunk and self.window is not None:
+            raise ValueError("a layer's mask is a window or chunks, not both")
+        if self.conv_path:
+            if not self.own_kv or self.qk_norm or self.out_gate or self.cos_sin_scale != 1.0:
+                raise ValueError("the convolution path takes none of own_kv=False, qk_norm, out_gate, scaled cos and sin")
+            if not (0 < self.hd <= 256 and 0 < self.vd <= 256):
+                raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels take up to 256")
+            self.prepared = False
+        elif (self.chunk or self.softcap or self.sink) and not self.prepared:
+            self.prepared = True          # the path whose every step takes the kernels with these options
         if self.prepared:
             if not self.own_kv:
                 raise ValueError("a layer that reads another layer's cache takes none of value_dim, qk_norm, out_gate")
             if not (0 < self.hd <= 256 and 0 < self.vd <= 256):
                 raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels take up to 256")
-        elif self.hd % 16 or not 16 <= self.hd <= 256:
+        elif not self.conv_path and (self.hd % 16 or not 16 <= self.hd <= 256):
             raise ValueError(f"head_dim {self.hd}: the attention kernels take multiples of 16 from 16 to 256")
         if self.window is not None and self.window <= 0:
             raise ValueError("window must be positive")
@@ -104,11 +143,22 @@ class GQAttention(Part):
             t[n["k_norm"]] = TensorSpec((self.hd,), init="ones", vector=True)
         if self.out_gate:
             t[n["gate"]] = TensorSpec((self.nh * self.vd, self.hidden))
+        if self.o_bias:
+            t[n["o_bias"]] = TensorSpec((self.hidden,), init="zeros", vector=True)
+        if self.taps:
+            t[n["q_conv"]] = TensorSpec((self.nh * self.hd, self.taps))
+            t[n["k_conv"]] = TensorSpec((self.nkv * self.hd, self.taps))
+            t[n["v_conv"]] = TensorSpec((self.nkv * self.vd, self.taps))
         t.update(self.position.tensors())
         return t
 
     def kv_request(self):
-        return KVRequest(self.nkv, self.width, self.window)
+        # (chunks: no query looks further back than its chunk's start, so a ring of one chunk is enough)
+        return KVRequest(self.nkv, self.width, self.window if not self.chunk else self.chunk)
+
+    @property
+    def channels(self):
+        return (self.nh + self.nkv) * self.hd + self.nkv * self.vd
 
     def describe(self):
         d = f"GQA({self.nh} q / {self.nkv} kv heads, head_dim={self.hd}{', bias' if self.bias else ''})"
@@ -118,7 +168,17 @@ class GQAttention(Part):
             d += ", q/k RMS norm"
         if self.out_gate:
             d += ", sigmoid output gate"
+        if self.taps:
+            d += f", convolution of {self.taps} taps on q, k, v"
         d += f", {self.position.describe()}"
+        if self.unit_norm:
+            d += ", q/k unit RMS after the rotation"
+        if self.softcap:
+            d += f", scores capped at {self.softcap:g}"
+        if self.sink:
+            d += ", softmax with a sink"
+        if self.chunk:
+            d += f", chunks of {self.chunk}"
         if self.window:
             d += f", window {self.window}"
         if not self.own_kv:
@@ -126,6 +186,12 @@ class GQAttention(Part):
         return d
 
     def state_request(self):
+        """The last taps - 1 projected rows [q | k | v] of a sequence, which the convolution of its next
+        tokens reads."""
+        if self.taps > 1:
+            from ..cache.kv import StateRequest
+
+            return StateRequest(((self.taps - 1) * self.channels,), torch.float32)
         return None
 
     def bind(self, tensors, rt):
@@ -144,6 +210,10 @@ class GQAttention(Part):
                 bs.append(torch.zeros(self.nh * self.vd, dtype=torch.float32, device=bs[0].device))
             self.bqkv = torch.cat(bs).contiguous()
         self.wo = tensors[n["o"]].contiguous()
+        self.bo = tensors[n["o_bias"]].to(torch.float32).contiguous() if self.o_bias else None
+        self.taps_w = None
+        if self.taps:
+            self.taps_w = torch.cat([tensors[n[r + "_conv"]].to(torch.float32) for r in ("q", "k", "v")], dim=0).contiguous()
         self.q_norm_w = self.k_norm_w = None
         if self.qk_norm:
             self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
@@ -151,7 +221,7 @@ class GQAttention(Part):
         self.position.bind(tensors, rt)
         self.scale = (float(self.fixed_scale) if self.fixed_scale is not None
                       else self.position.attention_scale() / math.sqrt(self.hd))
-        if self.prepared:
+        if self.prepared or self.conv_path:
             self.width = record_width(self.hd, self.vd, rt.is_bf16)
         # Single-token steps append in heads_prepare and attend with the split kernel, whose merge gates
         # and packs (three launches).  MOE_B200_PREPARED_FUSED=1 takes the fused decode kernel instead
@@ -179,9 +249,10 @@ class GQAttention(Part):
             core.heads_prepare(proj, batch.pos, batch.seq_of_token, q=row[:, :nh], k=row[:, nh:nh + nkv],
                                v=row[:, nh + nkv:], **prep)
             packed = rt.empty((T, nh * self.vd))
-            if core.attention_decode_fused(row.view(T, -1), None, 0, cache_view, batch, packed, nh=nh, window=self.window,
-                                           scale=self.scale, status=rt.status, gate=gate, dv=self.vd):
-                return linear(rt, packed, self.wo)
+            if self.plain_scores and core.attention_decode_fused(
+                    row.view(T, -1), None, 0, cache_view, batch, packed, nh=nh, window=self.window, scale=self.scale,
+                    status=rt.status, gate=gate, dv=self.vd):
+                return linear(rt, packed, self.wo, bias=self.bo)
             self._fused_decode = False       # a head size the fused kernel does not take
         q = rt.empty((T, nh, D))
         k_new, v_new = rt.empty((T, nkv, D)), rt.empty((T, nkv, D))
@@ -193,15 +264,41 @@ class GQAttention(Part):
         early = batch.all_decode or batch.all_fresh
         core.heads_prepare(proj, batch.pos, batch.seq_of_token, q=q, k=k_new, v=v_new,
                            commit=(cache_view, batch) if early else None, **prep)
+        return self._attend_prepared(rt, batch, cache_view, q, k_new, v_new, ctx, gate, early)
+
+    def _forward_conv(self, rt, h, batch, cache_view, state):
+        """Projection -> convolution over time (with the sequence's state), rotation of pairs
+        (2i, 2i + 1), unit norm, split and append -> attention over records of width D -> packing ->
+        output projection."""
+        T, D, nh, nkv = batch.num_tokens, self.width, self.nh, self.nkv
+        proj = linear(rt, h.act, self.wqkv, bias=self.bqkv)
+        table, rot = self.position.rotary_table()
+        q = rt.empty((T, nh, D))
+        k_new, v_new = rt.empty((T, nkv, D)), rt.empty((T, nkv, D))
+        ctx = rt.empty((T, nh, D))
+        if getattr(batch, "has_padding", False) and not batch.all_decode:
+            ctx.zero_()
+        early = batch.all_decode or batch.all_fresh
+        core.conv_heads_prepare(proj, batch, nh=nh, nkv=nkv, d=self.hd, dv=self.vd, width=D, q=q, k=k_new, v=v_new,
+                                taps_w=self.taps_w, state=state, eps=float((self.unit_norm or {}).get("eps", 0.0)),
+                                unit_norm=bool(self.unit_norm), freq=table, rot=rot,
+                                commit=cache_view if early else None, status=rt.status)
+        if self.taps > 1:
+            core.conv_state_update(proj, state, batch, taps=self.taps, channels=self.channels)
+        return self._attend_prepared(rt, batch, cache_view, q, k_new, v_new, ctx, None, early)
+
+    def _attend_prepared(self, rt, batch, cache_view, q, k_new, v_new, ctx, gate, early):
+        """Attention over prepared records of width D, packing (and gate), output projection."""
+        T, D, nh, nkv = batch.num_tokens, self.width, self.nh, self.nkv
         if batch.all_decode:
             # (the merge of the splits multiplies by the gate and packs the heads)
             packed = rt.empty((T, nh * self.vd))
             core.attention_decode(q, cache_view, batch, packed, nh=nh, window=self.window, scale=self.scale,
-                                  status=rt.status, gate=gate, dv=self.vd)
-            return linear(rt, packed, self.wo)
+                                  status=rt.status, gate=gate, dv=self.vd, **self.variant)
+            return linear(rt, packed, self.wo, bias=self.bo)
         else:
             done = False
-            if rt.is_bf16:
+            if rt.is_bf16 and self.plain_scores:
                 from ..ops import tc
 
                 if batch.all_fresh:
@@ -211,7 +308,7 @@ class GQAttention(Part):
                     done = tc.attention_cached(q, k_new, v_new, cache_view, batch, ctx, nh=nh, window=self.window,
                                                scale=self.scale, status=rt.status)
             if not done:
-                kw = dict(nh=nh, window=self.window, scale=self.scale, use_local=True, status=rt.status)
+                kw = dict(nh=nh, window=self.window, scale=self.scale, use_local=True, status=rt.status, **self.variant)
                 if not core.attention_tiled(q, k_new, v_new, cache_view, batch, ctx, **kw):
                     core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, **kw)
             if not early:
@@ -221,9 +318,11 @@ class GQAttention(Part):
             core.gate_pack(ctx, packed, nh=nh, dv=self.vd, width=D, gate=gate)
         else:
             packed = ctx.view(T, nh * D)
-        return linear(rt, packed, self.wo)
+        return linear(rt, packed, self.wo, bias=self.bo)
 
     def forward(self, rt, h, batch, cache_view, state=None):
+        if self.conv_path:
+            return self._forward_conv(rt, h, batch, cache_view, state)
         if self.prepared:
             return self._forward_prepared(rt, h, batch, cache_view)
         T = batch.num_tokens
@@ -240,13 +339,13 @@ class GQAttention(Part):
             # merge in ONE launch where the head size allows it
             if core.attention_decode_fused(qkv, table, rot, cache_view, batch, ctx, nh=self.nh, window=self.window,
                                            scale=self.scale, status=rt.status):
-                return linear(rt, ctx, self.wo)
+                return linear(rt, ctx, self.wo, bias=self.bo)
             # else: rotate and append in one launch, then attend over the cache alone
             q = rt.empty((T, self.nh, self.hd))
             core.rope_commit(qkv, batch.pos, table, self.nh, nkv, self.hd, rot, q, cache_view, batch, rt.status)
             core.attention_decode(q, cache_view, batch, ctx, nh=self.nh, window=self.window, scale=self.scale,
                                   status=rt.status)
-            return linear(rt, ctx, self.wo)
+            return linear(rt, ctx, self.wo, bias=self.bo)
         q = rt.empty((T, self.nh, self.hd))
         k_new = rt.empty((T, max(nkv, 1), self.hd))
         v_new = rt.empty((T, max(nkv, 1), self.hd))
@@ -283,7 +382,7 @@ class GQAttention(Part):
                     core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, **kw)
             if self.own_kv and not committed:
                 core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
-        return linear(rt, ctx, self.wo)
+        return linear(rt, ctx, self.wo, bias=self.bo)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -16,6 +16,7 @@ Interfaces by category
   ffn       forward(rt, h: Activations, batch) -> delta [T, hidden] float32;  wants32: bool
             optional: forward_lazy(rt, h, batch) -> delta or LazyDelta;
                       forward_prenorm(rt, x, delta, norm, batch) -> delta, LazyDelta, or None (not taken)
+  scale     vector(rt) -> float32 [size]: a per-channel factor on a sublayer's output
   block     forward(rt, x, pending, batch, cache_view, state) -> (x, pending)
 A pending delta may be a ``LazyDelta``; ``delta_for(norm, delta, rt)`` gives what a norm can take.
 """
@@ -52,6 +53,23 @@ class PostNormDelta(LazyDelta):
 
     def materialize(self, rt) -> torch.Tensor:
         return self.norm.normed32(rt, self.tensor)
+
+
+class ScaledPairDelta(LazyDelta):
+    """The outputs a and b of two sublayers that read the same input (b may be None), each still to
+    be multiplied by a per-channel factor: delta = a * sa + b * sb.  An RMS norm forms the sum, the
+    residual sum and itself in one kernel."""
+
+    kind = "scaled_pair"
+
+    def __init__(self, a, sa, b=None, sb=None):
+        self.a, self.sa, self.b, self.sb = a, sa, b, sb
+
+    def materialize(self, rt) -> torch.Tensor:
+        out = self.a * self.sa
+        if self.b is not None:
+            out.addcmul_(self.b, self.sb)
+        return out
 
 
 def delta_for(norm, delta, rt):

@@ -10,11 +10,19 @@ reads and writes the stream once instead of twice.
     x += post1(mixer(norm1(x)));  x += post2(ffn(norm2(x)))
 A sublayer's output is handed on together with its post-norm (``PostNormDelta``), so the next norm
 before a sublayer may form post-norm, residual sum and its own norm in one kernel.
+
+"Parallel": ONE norm, whose output both sublayers read, and one residual sum; each sublayer's output
+may be multiplied by a per-channel factor first, and the feed-forward is optional:
+    n = norm1(x);  x += scale1 * mixer(n) + scale2 * ffn(n)
+The two outputs are handed on unscaled and unsummed (``ScaledPairDelta``): the next norm forms the
+scaling, the sums and itself in one kernel.
 """
 from __future__ import annotations
 
 from ..config.spec import LayerSpec
-from .base import PostNormDelta, delta_for, make_part
+import torch
+
+from .base import PostNormDelta, ScaledPairDelta, delta_for, make_part
 
 
 class PreNormBlock:
@@ -78,7 +86,43 @@ class SandwichBlock:
         return x, PostNormDelta(self.ffn.forward(rt, h, batch), self.post2)
 
 
-_BLOCKS = {"prenorm": PreNormBlock, "sandwich": SandwichBlock}
+class ParallelBlock:
+    category, kind = "block", "parallel"
+
+    def __init__(self, layer: LayerSpec):
+        if layer.norm2 is not None or layer.post1 is not None or layer.post2 is not None:
+            raise ValueError("a parallel block has one norm, before both sublayers")
+        if layer.ffn is None and layer.scale2 is not None:
+            raise ValueError("a parallel block without a feed-forward has no factor for it")
+        self.layer = layer
+        self.norm1 = make_part("norm", layer.norm1)
+        self.mixer = make_part("mixer", layer.mixer)
+        self.ffn = make_part("ffn", layer.ffn) if layer.ffn is not None else None
+        self.scale1 = make_part("scale", layer.scale1) if layer.scale1 is not None else None
+        self.scale2 = make_part("scale", layer.scale2) if layer.scale2 is not None else None
+        self._ones = None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.ffn, self.scale1, self.scale2) if p is not None]
+
+    def _factor(self, rt, scale, like):
+        if scale is not None:
+            return scale.vector(rt)
+        if self._ones is None:
+            self._ones = torch.ones(like.shape[1], dtype=torch.float32, device=like.device)
+        return self._ones
+
+    def forward(self, rt, x, pending, batch, cache_view, state):
+        want32 = getattr(self.mixer, "wants32", False) or getattr(self.ffn, "wants32", False)
+        h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt), want32=want32)
+        a = self.mixer.forward(rt, h, batch, cache_view, state)
+        if self.ffn is None:
+            return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a))
+        b = self.ffn.forward(rt, h, batch)
+        return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a), b, self._factor(rt, self.scale2, b))
+
+
+_BLOCKS = {"prenorm": PreNormBlock, "sandwich": SandwichBlock, "parallel": ParallelBlock}
 
 
 def register_block(kind: str, cls) -> None:

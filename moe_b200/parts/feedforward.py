@@ -24,7 +24,9 @@ def _fuse_rows(tensors):
 
 
 class DenseSwiGLU(Part):
-    """y = Wd (act(Wg n) * (Wu n)); ``activation`` is "silu" (the default) or "gelu_tanh"."""
+    """y = Wd f(Wg n, Wu n); ``activation`` names f: "silu" (the default) and "gelu_tanh" are
+    act(g) * u; "clamped_sigmoid" with its constant ``limit`` L is
+    min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)."""
 
     category, kind = "ffn", "dense_swiglu"
     graph_safe = True
@@ -38,6 +40,9 @@ class DenseSwiGLU(Part):
         self.activation = str(self.params.get("activation", "silu"))
         if self.activation not in core.GLU_ACTS:
             raise ValueError(f"dense gated feed-forward: activation '{self.activation}' is none of {sorted(core.GLU_ACTS)}")
+        self.limit = float(self.params.get("limit") or 0.0)
+        if self.activation == "clamped_sigmoid" and not self.limit > 0:
+            raise ValueError("dense gated feed-forward: 'clamped_sigmoid' needs a positive limit")
 
     def tensors(self):
         n = self.names
@@ -48,7 +53,8 @@ class DenseSwiGLU(Part):
         }
 
     def describe(self):
-        return f"dense {'SwiGLU' if self.activation == 'silu' else 'gated ' + self.activation} {self.size}"
+        return (f"dense {'SwiGLU' if self.activation == 'silu' else 'gated ' + self.activation} {self.size}"
+                + (f", limit {self.limit:g}" if self.limit else ""))
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
@@ -57,7 +63,7 @@ class DenseSwiGLU(Part):
         self.w_down = tensors[n["down"]].contiguous()
 
     def forward(self, rt, h, batch):
-        return linear(rt, swiglu_linear(rt, h.act, self.w_gu, self.activation), self.w_down)
+        return linear(rt, swiglu_linear(rt, h.act, self.w_gu, self.activation, self.limit), self.w_down)
 
 
 class CombineDelta(LazyDelta):
@@ -81,6 +87,12 @@ class RoutedExperts(Part):
     category, kind = "ffn", "routed_experts"
     graph_safe = True
     wants32 = True   # router logits are computed from the 32-bit normed state
+    # {e} in an expert's tensor name is its number; "router_bias" is read only with ``router_bias``
+    default_names = {"router": "gate.weight", "router_bias": "gate.bias",
+                     "expert_gate": "experts.{e}.gate_proj.weight", "expert_up": "experts.{e}.up_proj.weight",
+                     "expert_down": "experts.{e}.down_proj.weight",
+                     "shared_gate_proj": "shared_expert.gate_proj.weight", "shared_up": "shared_expert.up_proj.weight",
+                     "shared_down": "shared_expert.down_proj.weight", "shared_gate": "shared_expert_gate.weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -93,6 +105,7 @@ class RoutedExperts(Part):
         self.scale = float(p.get("routed_scaling_factor", 1.0))
         self.shared_size = int(p.get("shared_size", 0) or 0)
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_size > 0
+        self.router_bias = bool(p.get("router_bias", False))     # logits = Wr n + b
         if not 0 < self.k <= self.E:
             raise ValueError("top_k must lie in 1..num_experts")
         # Set to a list to record every routing decision as (expert ids [T, k], weights [T, k]);
@@ -111,21 +124,27 @@ class RoutedExperts(Part):
         # 32-bit activations split into three bfloat16 terms (35 -> about 15 us at 2,048 tokens)
         self.tc_router_tokens = int(os.environ.get("MOE_B200_TC_ROUTER_MIN", "257"))
 
+    def _expert(self, role, e):
+        return self.names[role].format(e=e)
+
     def tensors(self):
-        t = {"gate.weight": TensorSpec((self.E, self.hidden))}
+        t = {self.names["router"]: TensorSpec((self.E, self.hidden))}
         for e in range(self.E):
-            t[f"experts.{e}.gate_proj.weight"] = TensorSpec((self.size, self.hidden), sparse=True)
-            t[f"experts.{e}.up_proj.weight"] = TensorSpec((self.size, self.hidden), sparse=True)
-            t[f"experts.{e}.down_proj.weight"] = TensorSpec((self.hidden, self.size), sparse=True)
+            t[self._expert("expert_gate", e)] = TensorSpec((self.size, self.hidden), sparse=True)
+            t[self._expert("expert_up", e)] = TensorSpec((self.size, self.hidden), sparse=True)
+            t[self._expert("expert_down", e)] = TensorSpec((self.hidden, self.size), sparse=True)
         return self._common(t)
 
     def _common(self, t):
+        n = self.names
+        if self.router_bias:
+            t[n["router_bias"]] = TensorSpec((self.E,), init="zeros", vector=True)
         if self.shared_size:
-            t["shared_expert.gate_proj.weight"] = TensorSpec((self.shared_size, self.hidden))
-            t["shared_expert.up_proj.weight"] = TensorSpec((self.shared_size, self.hidden))
-            t["shared_expert.down_proj.weight"] = TensorSpec((self.hidden, self.shared_size))
+            t[n["shared_gate_proj"]] = TensorSpec((self.shared_size, self.hidden))
+            t[n["shared_up"]] = TensorSpec((self.shared_size, self.hidden))
+            t[n["shared_down"]] = TensorSpec((self.hidden, self.shared_size))
         if self.shared_gate:
-            t["shared_expert_gate.weight"] = TensorSpec((1, self.hidden))
+            t[n["shared_gate"]] = TensorSpec((1, self.hidden))
         return t
 
     def tensors_in(self, has):
@@ -134,12 +153,13 @@ class RoutedExperts(Part):
         ``experts.down_proj`` [E, hidden, size]; stacked ``experts.{gate,up,down}_proj`` of three
         dimensions; else one tensor per expert and projection."""
         E, n, H = self.E, self.size, self.hidden
+        router = self.names["router"]
         if has("experts.gate_up_proj"):
-            t = {"gate.weight": TensorSpec((E, H)), "experts.gate_up_proj": TensorSpec((E, 2 * n, H), sparse=True),
+            t = {router: TensorSpec((E, H)), "experts.gate_up_proj": TensorSpec((E, 2 * n, H), sparse=True),
                  "experts.down_proj": TensorSpec((E, H, n), sparse=True)}
             return self._common(t)
         if has("experts.gate_proj") and has("experts.up_proj"):
-            t = {"gate.weight": TensorSpec((E, H)), "experts.gate_proj": TensorSpec((E, n, H), sparse=True),
+            t = {router: TensorSpec((E, H)), "experts.gate_proj": TensorSpec((E, n, H), sparse=True),
                  "experts.up_proj": TensorSpec((E, n, H), sparse=True),
                  "experts.down_proj": TensorSpec((E, H, n), sparse=True)}
             return self._common(t)
@@ -147,6 +167,7 @@ class RoutedExperts(Part):
 
     def describe(self):
         return (f"{self.E} experts of {self.size}, top-{self.k}, softmax gate"
+                + (" with bias" if self.router_bias else "")
                 + (", renormalised" if self.norm_topk else "")
                 + (f", scaled by {self.scale:g}" if self.scale != 1.0 else "")
                 + (f", shared expert {self.shared_size}" + (" (gated)" if self.shared_gate else "")
@@ -169,7 +190,9 @@ class RoutedExperts(Part):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.w_router = tensors["gate.weight"].contiguous()
+        n = self.names
+        self.w_router = tensors[n["router"]].contiguous()
+        self.b_router = tensors[n["router_bias"]].to(torch.float32).contiguous() if self.router_bias else None
         dev = self.w_router.device
         # The device layout is [E, 2 * size, hidden] (rows [0, size) gate, [size, 2 size) up) and
         # [E, hidden, size], whatever the checkpoint's; tensors are fetched one at a time.
@@ -184,26 +207,24 @@ class RoutedExperts(Part):
             self.w_gu = torch.cat([g.to(dt), u.to(dt)], dim=1).contiguous()
             self.w_down = self.w_down.to(dt).contiguous()
         else:
-            first = tensors["experts.0.gate_proj.weight"]
+            first = tensors[self._expert("expert_gate", 0)]
             dt = first.dtype
             self.w_gu = torch.empty((self.E, 2 * self.size, self.hidden), dtype=dt, device=dev)
             self.w_down = torch.empty((self.E, self.hidden, self.size), dtype=dt, device=dev)
             for e in range(self.E):
-                for name, dst in ((f"experts.{e}.gate_proj.weight", self.w_gu[e, : self.size]),
-                                  (f"experts.{e}.up_proj.weight", self.w_gu[e, self.size:]),
-                                  (f"experts.{e}.down_proj.weight", self.w_down[e])):
-                    t = tensors[name]
+                for role in ("expert_gate", "expert_up", "expert_down"):
+                    t = tensors[self._expert(role, e)]
                     if t.dtype != dt:                  # a checkpoint of mixed dtypes: everything in 32-bit
                         self.w_gu, self.w_down, dt = self.w_gu.float(), self.w_down.float(), torch.float32
-                        dst = {"gate": self.w_gu[e, : self.size], "up": self.w_gu[e, self.size:],
-                               "down": self.w_down[e]}[name.split(".")[2].split("_")[0]]
+                    dst = {"expert_gate": self.w_gu[e, : self.size], "expert_up": self.w_gu[e, self.size:],
+                           "expert_down": self.w_down[e]}[role]
                     dst.copy_(t)
         self.ws_gu = self.ws_down = self.w_sgate = None
         if self.shared_size:
-            self.ws_gu = _fuse_rows([tensors["shared_expert.gate_proj.weight"], tensors["shared_expert.up_proj.weight"]])
-            self.ws_down = tensors["shared_expert.down_proj.weight"].contiguous()
+            self.ws_gu = _fuse_rows([tensors[n["shared_gate_proj"]], tensors[n["shared_up"]]])
+            self.ws_down = tensors[n["shared_down"]].contiguous()
         if self.shared_gate:
-            self.w_sgate = tensors["shared_expert_gate.weight"].reshape(-1).to(self.w_router.dtype).contiguous()
+            self.w_sgate = tensors[n["shared_gate"]].reshape(-1).to(self.w_router.dtype).contiguous()
         # For prompts the router's logits come from the tensor cores: the 32-bit activations as three
         # bfloat16 terms against the (bfloat16, hence exact) router rows, three times side by side.
         self.w_router3 = None
@@ -228,10 +249,11 @@ class RoutedExperts(Part):
                 if after_logits is not None:
                     after_logits()
                 core.router_topk(logits, self.k, self.norm_topk, self.scale, topk_idx, topk_w, num_experts=self.E,
-                                 shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
+                                 shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None), bias=self.b_router)
                 return topk_idx, topk_w, sg
         core.router(h.f32, self.w_router, self.k, self.norm_topk, self.scale, topk_idx, topk_w,
-                    shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None))
+                    shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None),
+                    bias=self.b_router)
         if after_logits is not None:
             after_logits()
         return topk_idx, topk_w, sg
@@ -251,7 +273,7 @@ class RoutedExperts(Part):
         tokens, norm, router and dispatch are one launch.  None if the sizes or the kind of norm do
         not allow it (the block then runs the norm itself and calls ``forward``)."""
         rms = getattr(norm, "rms_params", None)          # the norm says whether it can be run by a neighbour
-        if rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256:
+        if rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256 or self.b_router is not None:
             return None
         norm_w, norm_eps = rms()
         routed = core.norm_route(x, delta, norm_w, norm_eps, self.w_router, self.k, self.norm_topk, self.scale,
@@ -283,7 +305,8 @@ class RoutedExperts(Part):
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = core.route_dispatch(
                 h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,
                 seq_of_token=getattr(batch, "seq_of_token", None),
-                gather=h.act if h.act.dtype == torch.bfloat16 and T <= 16 else None, status=rt.status)
+                gather=h.act if h.act.dtype == torch.bfloat16 and T <= 16 else None, status=rt.status,
+                bias=self.b_router)
             # (more tokens: the gather by that one block would take longer than a launch of its own)
         else:
             def shared_beside():

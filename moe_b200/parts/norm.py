@@ -14,7 +14,8 @@ from .base import Activations, LazyDelta, Part, TensorSpec, register_part
 class RMSNorm(Part):
     category, kind = "norm", "rmsnorm"
     graph_safe = True
-    lazy_kinds = ("expert_combine",)      # deltas this norm forms inside its own kernel
+    lazy_kinds = ("expert_combine", "scaled_pair")      # deltas this norm forms inside its own kernel
+    default_names = {"weight": "weight"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -22,7 +23,7 @@ class RMSNorm(Part):
         self.eps = float(self.params["eps"])
 
     def tensors(self):
-        return {"weight": TensorSpec((self.size,), init="ones", vector=True)}
+        return {self.names["weight"]: TensorSpec((self.size,), init="ones", vector=True)}
 
     def describe(self):
         return f"RMSNorm eps {self.eps:g}"
@@ -35,7 +36,7 @@ class RMSNorm(Part):
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.weight = tensors[self.names["weight"]].to(torch.float32).contiguous()
 
     def normed32(self, rt, t):
         out = rt.empty(t.shape, torch.float32)
@@ -53,6 +54,11 @@ class RMSNorm(Part):
                 out32 = rt.empty((n, self.size), torch.float32)
         else:
             out32 = rt.empty((n, self.size), torch.float32)
+        if isinstance(delta, LazyDelta) and delta.kind == "scaled_pair":
+            # two sublayers' outputs times their per-channel factors, the residual sum and the norm
+            core.rmsnorm_scaled(x, delta.a, delta.sa, delta.b, delta.sb, self.weight, self.eps, rows=rows, out32=out32,
+                                out16=out16, write_back=write_back, status=rt.status)
+            return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
         if isinstance(delta, LazyDelta):
             if delta.kind != "expert_combine" or not core.rmsnorm_combine(
                     x, delta, self.weight, self.eps, rows=rows, out32=out32, out16=out16, write_back=write_back,
@@ -123,5 +129,31 @@ class DynamicTanh(Part):
         return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
 
 
+class ChannelScale(Part):
+    """A per-channel factor on a sublayer's output ("layer scale")."""
+
+    category, kind = "scale", "channel_scale"
+    graph_safe = True
+    default_names = {"weight": "weight"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(self.params["size"])
+
+    def tensors(self):
+        return {self.names["weight"]: TensorSpec((self.size,), init="ones", vector=True)}
+
+    def describe(self):
+        return "per-channel scale"
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors[self.names["weight"]].to(torch.float32).contiguous()
+
+    def vector(self, rt):
+        return self.weight
+
+
+register_part("scale", "channel_scale", ChannelScale)
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "dyt", DynamicTanh)

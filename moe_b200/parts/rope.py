@@ -2,7 +2,8 @@
 
 inv_freq[i] = theta^(-2 i / dim) for i < dim/2, computed in float32 as the
 reference does (src/spec.rs:89-96); the angle of position p is float32(p) *
-inv_freq[i] (src/model.rs:326-328).  Pairs are half-split: (i, i + dim/2).
+inv_freq[i] (src/model.rs:326-328).  Pairs are half-split, (i, i + dim/2), unless the
+part is given ``interleaved``: then pair i is (2i, 2i + 1).
 """
 from __future__ import annotations
 
@@ -30,13 +31,15 @@ class RotaryEncoding(Part):
         self.rotary_dim = int(self.params["rotary_dim"])
         if self.rotary_dim % 2:
             raise ValueError("rotary_dim must be even")
+        self.interleaved = bool(self.params.get("interleaved", False))
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.inv_freq = rotary_inv_freq(self.theta, self.rotary_dim).to(rt.device)
 
     def describe(self):
-        return f"rope theta {self.theta:.0f}" + (f" on {self.rotary_dim} dims" if self.params.get("partial") else "")
+        return (f"rope theta {self.theta:.0f}" + (f" on {self.rotary_dim} dims" if self.params.get("partial") else "")
+                + (", pairs (2i, 2i+1)" if self.interleaved else ""))
 
     def rotary_table(self):
         """(inv_freq, rotary_dim): lets the mixer rotate inside its own kernel."""

@@ -103,8 +103,10 @@ class WeightStore:
         wrong, wrong_dt = [], []
         for n, shp in expected.items():
             if n in have:
-                if tuple(self.shape(n)) != tuple(shp):
-                    wrong.append((n, tuple(self.shape(n)), tuple(shp)))
+                got = tuple(self.shape(n))
+                # (an expected extent of -1 is one that only the tensor itself gives)
+                if len(got) != len(tuple(shp)) or any(e != -1 and e != g for g, e in zip(got, shp)):
+                    wrong.append((n, got, tuple(shp)))
                 if self.stored_dtype(n) not in _FLOATS:
                     wrong_dt.append((n, str(self.stored_dtype(n))))
         if missing or unexpected or wrong or wrong_dt:
