@@ -40,7 +40,7 @@ wkv_shift_mix_kernel(const float* __restrict__ h, const float* __restrict__ mu, 
     const size_t plane = (size_t)num_tokens * width;
     if (s < 0) {
         for (int c = threadIdx.x; c < width; c += blockDim.x) {
-            for (int m = 0; m < streams; m++) st_f(out + m * plane + (size_t)t * width + c, 0.f);
+            for (int m = 0; m < streams - (last32 ? 1 : 0); m++) st_f(out + m * plane + (size_t)t * width + c, 0.f);
             if (last32) last32[(size_t)t * width + c] = 0.f;
         }
         return;
