@@ -181,7 +181,7 @@ def max_rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
 def routed_parts(model):
     """The routed feed-forwards in the order the schedule runs them."""
     return [model.blocks[e.layer].ffn for e in model.spec.schedule
-            if model.blocks[e.layer].ffn.kind == "routed_experts"]
+            if getattr(model.blocks[e.layer].ffn, "kind", None) == "routed_experts"]
 
 
 def whole_with_picks(engine, tokens: Sequence[int]):

@@ -76,10 +76,11 @@ def rotate_pairs(x, positions, r, base):
     return out
 
 
-def chunked_sink_attention(q, k, v, scale, softcap, chunk):
+def chunked_sink_attention(q, k, v, scale, softcap, chunk, sink=True):
     """q: [T, H, d], k: [T, G, d], v: [T, G, dv].  Query i sees key j <= i of its own chunk
     (i // chunk == j // chunk; every earlier key without chunks).  The scores pass
-    cap * tanh(s / cap) if a cap is given; the weights are exp(s_j) / (1 + sum_j exp(s_j))."""
+    cap * tanh(s / cap) if a cap is given; the weights are exp(s_j) / (1 + sum_j exp(s_j)) (the 1
+    is the sink; ``sink=False`` leaves it out, to show how much it matters)."""
     T, H, _ = q.shape
     _, G, dv = v.shape
     out = torch.zeros(T, H, dv, dtype=F)
@@ -94,7 +95,7 @@ def chunked_sink_attention(q, k, v, scale, softcap, chunk):
         if softcap:
             s = softcap * torch.tanh(s / softcap)
         e = torch.exp(s).masked_fill(~seen, 0.0)
-        out[:, h] = (e / (1.0 + e.sum(-1, keepdim=True))) @ v[:, g]
+        out[:, h] = (e / ((1.0 if sink else 0.0) + e.sum(-1, keepdim=True))) @ v[:, g]
     return out
 
 
@@ -160,14 +161,23 @@ def silu_glu(w, p, n):
     return (silu(n @ w[p + ".gate"].T) * (n @ w[p + ".up"].T)) @ w[p + ".down"].T
 
 
-def routed_experts(w, p, mlp, n, picks=None, forced=None):
+def routed_experts(w, p, mlp, n, picks=None, forced=None, margins=None):
     """Every token takes the ``top`` experts of largest router logit, weighted by the softmax over
     those logits alone; a shared expert, if any, is added for every token.  ``picks`` (a list)
     receives the chosen experts [T, top]; ``forced`` replaces the choice (the weights still come from
-    the logits), for comparisons with an implementation whose near-ties fall the other way."""
+    the logits), for comparisons with an implementation whose near-ties fall the other way;
+    ``margins`` (a list) then receives, for every token whose forced choice differs from the free one,
+    the gap between the logits that were swapped as a fraction of the logits' root mean square."""
     E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
     z = n @ w[p + ".router"].T + w[p + ".router.b"]
-    idx = torch.topk(z, top, dim=-1).indices if forced is None else forced
+    free = torch.topk(z, top, dim=-1).indices
+    idx = free if forced is None else torch.as_tensor(forced, dtype=torch.long)
+    if forced is not None and margins is not None:
+        rms = float(z.pow(2).mean().sqrt().clamp(min=1e-30))
+        for t in range(z.shape[0]):
+            a, b = set(free[t].tolist()), set(idx[t].tolist())
+            if a != b:
+                margins.append((max(float(z[t, e]) for e in a - b) - min(float(z[t, e]) for e in b - a)) / rms)
     if picks is not None:
         picks.append(idx.clone())
     weight = torch.softmax(torch.gather(z, 1, idx), dim=-1)
@@ -182,9 +192,10 @@ def routed_experts(w, p, mlp, n, picks=None, forced=None):
 
 
 # --------------------------------------------------------------------------- the model
-def forward(cfg, w, tokens, layers_out=None, picks=None, forced=None):
+def forward(cfg, w, tokens, layers_out=None, picks=None, forced=None, margins=None):
     """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the stream after
-    every layer; ``picks`` / ``forced``: the routed layers' choices, in layer order."""
+    every layer; ``picks`` / ``forced`` / ``margins``: the routed layers' choices, in layer order
+    (see ``routed_experts``)."""
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][torch.tensor(tokens)] * float(cfg["embedding"]["scale"])
     forced = list(forced) if forced is not None else None
@@ -203,7 +214,7 @@ def forward(cfg, w, tokens, layers_out=None, picks=None, forced=None):
             if mlp["kind"] == "dense":
                 b = clamped_glu(w, p + ".mlp", n, float(mlp["limit"]))
             elif mlp["kind"] == "moe":
-                b = routed_experts(w, p + ".mlp", mlp, n, picks, forced.pop(0) if forced is not None else None)
+                b = routed_experts(w, p + ".mlp", mlp, n, picks, forced.pop(0) if forced is not None else None, margins)
             else:
                 raise ValueError(mlp["kind"])
             delta = delta + b * w[p + ".ls2"]
