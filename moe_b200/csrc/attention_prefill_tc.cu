@@ -2,7 +2,8 @@
 // head sizes 64 and 128: whole prompts, and sequences that go on from the cache.
 //
 // Same formulas as attention_prefill.cu (reference: src/model.rs:794-827): causal, optional window
-// [p + 1 - w, p], scale 1/sqrt(d), kv head = head / (heads / kv_heads); scores, running maximum
+// [p + 1 - w, p] (or the chunk of p, capped scores and a softmax with a sink: AttnVariant in
+// common.cuh), scale 1/sqrt(d), kv head = head / (heads / kv_heads); scores, running maximum
 // and sum, and the output accumulator are float32; P enters the second product as two bfloat16
 // terms (head and remainder), i.e. with 16 bits.
 //
@@ -190,7 +191,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                        const __grid_constant__ CUtensorMap tmVc, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                        const int* __restrict__ slots, const int* __restrict__ tables, int table_stride, int ring,
-                       int num_pages, int num_seqs, int nh, int nkv, int window, float scale_log2, int* status) {
+                       int num_pages, int num_seqs, int nh, int nkv, int window, float scale_log2, int* status,
+                       const AttnVariant av) {
     constexpr int CH = HD / 64;                      // 128-byte chunks of a row
     constexpr int TILE_BYTES = CH * 128 * 128;       // a 128-row operand tile
     constexpr int STAGE_BYTES = 2 * TILE_BYTES;      // K, then V
@@ -228,10 +230,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // start + q0 + r.  Key tiles: `nc` tiles of absolute positions [kt_lo * KT, ...) below `start`
     // from the cache, then tiles t_lo ... of the step's own tokens.
     const int start = seq_start ? seq_start[seq] : 0;
-    const int lo_pos = window > 0 ? max(0, start + q0 + 1 - window) : 0;      // oldest key any row of the tile sees
+    const int lo_pos = attn_lo(start + q0, window, av.chunk);                 // oldest key any row of the tile sees
     const int kt_lo = lo_pos / KT;
     const int nc = lo_pos < start ? (start - 1) / KT - kt_lo + 1 : 0;
-    const int t_lo = window > 0 ? max(0, q0 + 1 - window) / KT : 0;
+    const int t_lo = max(0, lo_pos - start) / KT;
     const int n_tiles = nc + q_last / KT - t_lo + 1;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -400,6 +402,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const uint32_t lane_base = (uint32_t)(qd * 32) << 16;
         const int row = q0 + r;                                // this thread's query among the step's tokens
         const int prow = start + row;                          // and its position
+        const int lo_row = attn_lo(prow, window, av.chunk);    // the oldest key it sees
+        // a capped score cap * tanh(s * scale / cap), in units of log 2: cap_log2 * tanh(s * cap_in)
+        const float cap_log2 = av.softcap * 1.4426950408889634f;
+        const float cap_in = av.softcap > 0.f ? scale_log2 / cap_log2 : 0.f;
+        // tanh(x) = 1 - 2 / (exp(2x) + 1), with the exponential of the hardware: a few units in the last place
+        auto capped = [&](float raw) {
+            const float e = ex2_approx(raw * cap_in * 2.8853900817779268f);
+            return cap_log2 * (1.0f - __fdividef(2.0f, e + 1.0f));
+        };
         const uint32_t to = tmem + COL_O + lane_base + half * (HD / 2);
         float m = -INFINITY, l = 0.f;
         bool ok = true;
@@ -415,10 +426,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             const int jh = j0 + half * (KT / 2);
             // a tile strictly below the diagonal, inside the window and inside the sequence needs no mask
             const bool full = j0 + KT - 1 <= start + q0 && j0 + KT <= jmax &&
-                              (window <= 0 || j0 >= start + q0 + QT - window);
+                              (av.chunk > 0 ? j0 >= attn_lo(start + q0 + QT - 1, 0, av.chunk)
+                                            : (window <= 0 || j0 >= start + q0 + QT - window));
             auto tile_softmax = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
-                auto visible = [&](int j) { return j <= prow && j < jmax && (window <= 0 || j >= prow + 1 - window); };
+                auto visible = [&](int j) { return j <= prow && j < jmax && j >= lo_row; };
                 // pass 1: the maximum of the half row (of the raw scores: the scale is positive)
                 float mx0 = -INFINITY, mx1 = -INFINITY;
                 {
@@ -440,7 +452,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(x_bar(qd));
                 if (!mbar_wait(x_bar(qd), it & 1, &s_abort, status, 0x4a)) return false;
-                const float mx = fmaxf(x_max[b][0][r], x_max[b][1][r]) * scale_log2;
+                // (a capped score grows with the raw one, so the largest raw score gives the largest capped one)
+                const float mx_raw = fmaxf(x_max[b][0][r], x_max[b][1][r]);
+                const float mx = av.softcap > 0.f ? (mx_raw == -INFINITY ? -INFINITY : capped(mx_raw)) : mx_raw * scale_log2;
                 // The running maximum only has to keep the exponentials in range: it moves when the
                 // tile's maximum exceeds it by more than 8 (a factor 256), which spares most rescalings.
                 float m_new = m, alpha = 1.f;
@@ -478,7 +492,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float x0 = fmaf(sc[i], scale_log2, neg_m), x1 = fmaf(sc[i + 1], scale_log2, neg_m);
+                        float x0, x1;
+                        if (av.softcap > 0.f)
+                            x0 = capped(sc[i]) + neg_m, x1 = capped(sc[i + 1]) + neg_m;
+                        else
+                            x0 = fmaf(sc[i], scale_log2, neg_m), x1 = fmaf(sc[i + 1], scale_log2, neg_m);
                         if (MASKED) {
                             if (!visible(jh + c * 32 + i)) x0 = -INFINITY;
                             if (!visible(jh + c * 32 + i + 1)) x1 = -INFINITY;
@@ -505,7 +523,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         // the row's sum: the two halves, in a fixed order
         if (ok) {
-            x_sum[half][r] = l;
+            // (a sink: one more term of score 0, which carries no value; both halves hold the same m)
+            x_sum[half][r] = (av.sink && half == 0 && m != -INFINITY) ? l + ex2_approx(-m) : l;
             __syncwarp();
             if (lane == 0) mbar_arrive(x_bar(qd));
             ok = mbar_wait(x_bar(qd), n_tiles & 1, &s_abort, status, 0x4c);
@@ -601,7 +620,7 @@ struct CacheArgs {
 template <int HD>
 int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const CacheArgs& c, void* out,
            const int* cu_seqlens, int num_seqs, int num_tokens, int nh, int nkv, int window, float scale, int* status,
-           cudaStream_t stream) {
+           const AttnVariant av, cudaStream_t stream) {
     constexpr int TILE_BYTES = (HD / 64) * 128 * 128;
     const int smem = 5 * TILE_BYTES + 1024 + 192;
     static bool configured = false;
@@ -613,19 +632,20 @@ int launch(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tm
     dim3 grid(((num_tokens + QT - 1) / QT + num_seqs) * nh);
     return launch_pdl(attn_prefill_tc_kernel<HD>, grid, 320, (size_t)smem, stream, tmQ, tmK, tmV, c.tmK, c.tmV,
                       (__nv_bfloat16*)out, cu_seqlens, c.seq_start, c.slots, c.tables, c.table_stride, c.ring,
-                      c.num_pages, num_seqs, nh, nkv, window, scale * 1.4426950408889634f, status);
+                      c.num_pages, num_seqs, nh, nkv, window, scale * 1.4426950408889634f, status, av);
 }
 
 int run(const void* q, const void* k, const void* v, CacheArgs& c, void* out, const int* cu_seqlens, int num_seqs,
-        int num_tokens, int nh, int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+        int num_tokens, int nh, int nkv, int hd, int window, float scale, int* status, const AttnVariant av,
+        cudaStream_t stream) {
     CUtensorMap tmQ, tmK, tmV;
     if (!make_map(&tmQ, q, num_tokens, nh, hd) || !make_map(&tmK, k, num_tokens, nkv, hd) ||
         !make_map(&tmV, v, num_tokens, nkv, hd))
         return -1;
     if (!c.seq_start) c.tmK = tmK, c.tmV = tmV;         // never used: no tile comes from the cache
     if (hd == 64)
-        return launch<64>(tmQ, tmK, tmV, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
-    return launch<128>(tmQ, tmK, tmV, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, stream);
+        return launch<64>(tmQ, tmK, tmV, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, av, stream);
+    return launch<128>(tmQ, tmK, tmV, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, window, scale, status, av, stream);
 }
 
 }  // namespace
@@ -635,13 +655,14 @@ int run(const void* q, const void* k, const void* v, CacheArgs& c, void* out, co
 // does not take: the caller then uses moe_attention_prefill_bf16.
 MOE_API int moe_attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens,
                                      int num_seqs, int num_tokens, int nh, int nkv, int hd, int window, float scale,
-                                     int* status, cudaStream_t stream) {
+                                     int* status, int chunk, float softcap, int sink, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
     if (hd != 64 && hd != 128) return -1;
     if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) != 0) return -1;
     CacheArgs c{};
-    return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status, stream);
+    return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status,
+               AttnVariant{chunk, softcap, sink}, stream);
 }
 
 // The same for sequences that go on from the cache: sequence i held seq_start[i] tokens before the
@@ -654,7 +675,7 @@ MOE_API int moe_attention_cached_tc(const void* q, const void* k, const void* v,
                                     const void* v_cache, void* out, const int* cu_seqlens, const int* seq_start,
                                     const int* slots, const int* tables, int table_stride, int ring, int page_size,
                                     int num_pages, int num_seqs, int num_tokens, int nh, int nkv, int hd, int window,
-                                    float scale, int* status, cudaStream_t stream) {
+                                    float scale, int* status, int chunk, float softcap, int sink, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || num_pages <= 0) return (int)cudaErrorInvalidValue;
     if (!seq_start || !slots || !tables || !k_cache || !v_cache) return (int)cudaErrorInvalidValue;
@@ -668,5 +689,6 @@ MOE_API int moe_attention_cached_tc(const void* q, const void* k, const void* v,
     if (!make_cache_map(&c.tmK, k_cache, (long long)num_pages * nkv * 64, hd) ||
         !make_cache_map(&c.tmV, v_cache, (long long)num_pages * nkv * 64, hd))
         return -1;
-    return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status, stream);
+    return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status,
+               AttnVariant{chunk, softcap, sink}, stream);
 }

@@ -35,9 +35,9 @@ def lib():
 
         L.moe_attention_prefill_bf16.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P]
         L.moe_attention_prefill_bf16.restype = c_int
-        L.moe_attention_prefill_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P, P]
+        L.moe_attention_prefill_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P, I, c_float, I, P]
         L.moe_attention_prefill_tc.restype = c_int
-        L.moe_attention_cached_tc.argtypes = [P] * 10 + [I] * 10 + [c_float, P, P]
+        L.moe_attention_cached_tc.argtypes = [P] * 10 + [I] * 10 + [c_float, P, I, c_float, I, P]
         L.moe_attention_cached_tc.restype = c_int
         L.moe_tc_set_pdl.argtypes = [c_int]
         L.moe_tc_set_pdl.restype = None
@@ -196,19 +196,28 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
 
 
 def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, out: torch.Tensor, *, nh: int, nkv: int,
-                      hd: int, window, scale: float, status=None) -> bool:
+                      hd: int, window, scale: float, status=None, chunk=0, softcap=0.0, sink=False) -> bool:
     """Causal (optionally windowed) attention of whole prompts on the tensor cores; every
     sequence of ``batch`` must start at position 0.  False if the head size is not taken.
-    Head sizes 64 and 128 run on tcgen05 (``attention_prefill_tc.cu``), 16 and 32 on mma.sync."""
+    Head sizes 64 and 128 run on tcgen05 (``attention_prefill_tc.cu``), 16 and 32 on mma.sync.
+    ``chunk``, ``softcap``, ``sink``: as in ``core.attention_generic``; only the tcgen05 kernel
+    takes them."""
     if q.dtype != torch.bfloat16 or hd not in (16, 32, 64, 128):
+        return False
+    variant = core._variant(chunk, softcap, sink)
+    plain = variant == (0, 0.0, 0)
+    if not plain and not (hd in (64, 128) and status is not None and _ATTN_TC):
         return False
     if hd in (64, 128) and status is not None and _ATTN_TC:
         code = lib().moe_attention_prefill_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                               batch.cu_seqlens.data_ptr(), batch.num_seqs, batch.num_tokens, nh, nkv,
-                                              hd, int(window or 0), float(scale), status.data_ptr(), core._stream())
+                                              hd, int(window or 0), float(scale), status.data_ptr(), *variant,
+                                              core._stream())
         if code != -1:
             core._ok(code, "attention_prefill_tc")
             return True
+        if not plain:
+            return False
     code = lib().moe_attention_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                             batch.cu_seqlens.data_ptr(), batch.num_seqs, batch.num_tokens, nh, nkv,
                                             hd, int(window or 0), float(scale), core._stream())
@@ -219,7 +228,7 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, 
 
 
 def attention_cached(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, view, batch, out: torch.Tensor, *,
-                     nh: int, window, scale: float, status) -> bool:
+                     nh: int, window, scale: float, status, chunk=0, softcap=0.0, sink=False) -> bool:
     """Causal (optionally windowed) attention of a step whose sequences go on from the cache, on
     tcgen05: the keys before the step from the pages of ``view`` (one layer's cache), the step's own
     from ``k_new`` / ``v_new``.  False, with nothing launched, for what the kernel does not take
@@ -233,7 +242,7 @@ def attention_cached(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, 
                                          batch.seq_start.data_ptr(), batch.slots.data_ptr(), g.table.data_ptr(),
                                          g.table.stride(0), g.ring, g.page_size, g.num_pages, batch.num_seqs,
                                          batch.num_tokens, nh, g.num_kv_heads, hd, int(window or 0), float(scale),
-                                         status.data_ptr(), core._stream())
+                                         status.data_ptr(), *core._variant(chunk, softcap, sink), core._stream())
     if code == -1:
         return False
     core._ok(code, "attention_cached_tc")

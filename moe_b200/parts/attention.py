@@ -98,7 +98,7 @@ class GQAttention(Part):
                              or self.cos_sin_scale != 1.0)
         self.conv_path = bool(self.taps or self.unit_norm or getattr(self.position, "interleaved", False))
         self.variant = dict(chunk=self.chunk, softcap=self.softcap, sink=self.sink)
-        self.plain_scores = not (self.chunk or self.softcap or self.sink)    # what the tensor-core kernels compute
+        self.plain_scores = not (self.chunk or self.softcap or self.sink)    # what the fused decode kernel computes
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if self.chunk < 0 or self.softcap < 0 or self.taps < 0 or self.taps > 16:
@@ -298,15 +298,15 @@ class GQAttention(Part):
             return linear(rt, packed, self.wo, bias=self.bo)
         else:
             done = False
-            if rt.is_bf16 and self.plain_scores:
+            if rt.is_bf16:
                 from ..ops import tc
 
                 if batch.all_fresh:
                     done = tc.attention_prefill(q, k_new, v_new, batch, ctx, nh=nh, nkv=nkv, hd=D, window=self.window,
-                                                scale=self.scale, status=rt.status)
+                                                scale=self.scale, status=rt.status, **self.variant)
                 else:
                     done = tc.attention_cached(q, k_new, v_new, cache_view, batch, ctx, nh=nh, window=self.window,
-                                               scale=self.scale, status=rt.status)
+                                               scale=self.scale, status=rt.status, **self.variant)
             if not done:
                 kw = dict(nh=nh, window=self.window, scale=self.scale, use_local=True, status=rt.status, **self.variant)
                 if not core.attention_tiled(q, k_new, v_new, cache_view, batch, ctx, **kw):
