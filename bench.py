@@ -633,6 +633,198 @@ def run_supevik(args):
     return 0
 
 
+# Fogapel at sizes that resemble a real model's layers, and beside each the library's closest model at
+# equal size: Qwen2 MoE with as many layers, the same width, heads, head size, experts, expert and shared
+# sizes, first layer dense, and vocabulary (every layer of it is attention; its windows are the chunks' size).
+FOGAPEL_SHAPES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, rot=64, taps=4, softcap=30.0,
+                  wkv_heads=32, wkv_dim=64, ff=5632, limit=7.0, experts=32, top=4, expert_ff=704, shared_ff=2816,
+                  order=("wkv", "wkv", "attention", "wkv", "attention", "wkv"), vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=2048, rot=64, taps=4, softcap=30.0,
+                  wkv_heads=64, wkv_dim=64, ff=11008, limit=7.0, experts=32, top=4, expert_ff=1408, shared_ff=5632,
+                  order=("wkv", "attention", "wkv", "attention"), vocab=32768),
+}
+
+
+def fogapel_config(sh):
+    att = {"heads": sh["heads"], "kv_heads": sh["kv_heads"], "dim": sh["dim"], "vdim": sh["vdim"], "scale": sh["dim"] ** -0.5,
+           "softcap": sh["softcap"], "conv": sh["taps"], "mask": {"size": sh["chunk"]}, "rot": {"dims": sh["rot"], "base": 1e6}}
+    wkv = {"heads": sh["wkv_heads"], "dim": sh["wkv_dim"]}
+    moe = {"kind": "moe", "router": {"experts": sh["experts"], "top": sh["top"]}, "expert": {"ff": sh["expert_ff"]},
+           "shared": {"ff": sh["shared_ff"]}}
+    dense = {"kind": "dense", "ff": sh["ff"], "limit": sh["limit"]}
+    return {"architecture": "Fogapel", "vocab": sh["vocab"], "width": sh["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5},
+            "layers": [{"type": t, "mixer": att if t == "attention" else wkv, "mlp": dense if i == 0 else moe}
+                       for i, t in enumerate(sh["order"])]}
+
+
+def moe_qwen_config(sh):
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=len(sh["order"]),
+                hidden_size=sh["width"], num_attention_heads=sh["heads"], num_key_value_heads=sh["kv_heads"],
+                head_dim=sh["dim"], num_experts=sh["experts"], num_experts_per_tok=sh["top"],
+                moe_intermediate_size=sh["expert_ff"], shared_expert_intermediate_size=sh["shared_ff"],
+                norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[0], intermediate_size=sh["ff"],
+                vocab_size=sh["vocab"], rope_theta=1e6, rms_norm_eps=1e-5, use_sliding_window=True,
+                sliding_window=sh["chunk"], max_window_layers=0, tie_word_embeddings=False,
+                max_position_embeddings=8192, qkv_bias=True)
+
+
+def fogapel_kernels(sh, pk):
+    """The new design's own kernels beside the like kernels of the closest model, each alone at 8,192
+    tokens of 4 sequences (what a call reads and writes exceeds L2), as a fraction of the measured copy
+    bandwidth (attention: of the measured bf16 peak, counting the products of the keys a query sees)."""
+    import torch
+
+    import moe_b200
+    from moe_b200.cache.kv import KVCache, KVRequest
+    from moe_b200.ops import core, tc
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import gpu_util as G
+
+    dev = "cuda:0"
+    B, n = 4, 2048
+    T, H, nh, nkv, d = B * n, sh["width"], sh["heads"], sh["kv_heads"], sh["dim"]
+    wh, wd = sh["wkv_heads"], sh["wkv_dim"]
+    I = wh * wd
+    status = core.new_status(dev)
+    r = lambda *s: torch.randn(*s, device=dev)
+    out = {}
+
+    def row(name, ms, nbytes=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if nbytes:
+            e["gb_s"] = round(nbytes / ms / 1e6, 0)
+            e["of_copy_peak"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tflops"] = round(flops / ms / 1e9, 0)
+            e["of_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+        out[name] = e
+
+    batch = G.make_batch(dev, list(range(1, B + 1)), [0] * B, [n] * B)
+    # ---- norms -------------------------------------------------------------------------------------
+    x, a, b, w, sa, sb = r(T, H), r(T, H), r(T, H), r(H), r(H), r(H)
+    o16 = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    row("rmsnorm_scaled (two scaled outputs + sum + norm)",
+        _median_ms(lambda: core.rmsnorm_scaled(x, a, sa, b, sb, w, 1e-5, out16=o16, status=status)), T * H * (4 + 4 + 4 + 4 + 2))
+    row("rmsnorm (sum + norm)", _median_ms(lambda: core.rmsnorm(x, w, 1e-5, delta=a, out16=o16, status=status)), T * H * (4 + 4 + 4 + 2))
+    # ---- between projection and attention -------------------------------------------------------------
+    wq = (nh + 2 * nkv) * d
+    proj = r(T, wq)
+    q, k, v = (torch.empty((T, m, d), dtype=torch.bfloat16, device=dev) for m in (nh, nkv, nkv))
+    freq = torch.rand(sh["rot"] // 2, device=dev)
+    taps_w = r(sh["taps"], wq)
+    state = torch.zeros((B + 2, (sh["taps"] - 1) * wq), device=dev)
+    row("conv_heads_prepare (convolution + rotation + unit norm + split)", _median_ms(lambda: core.conv_heads_prepare(
+        proj, batch, nh=nh, nkv=nkv, d=d, dv=d, width=d, q=q, k=k, v=v, taps_w=taps_w, state=state, eps=1e-5, unit_norm=True,
+        freq=freq, rot=sh["rot"], status=status)), T * wq * (4 + 2))
+    row("rope_split (rotation + split)", _median_ms(lambda: core.rope_split(proj, batch.pos, freq, nh, nkv, d, sh["rot"], q, k, v)),
+        T * wq * (4 + 2))
+    # ---- attention of whole prompts: keys a query sees, 4 flops a key and dimension -------------------------
+    qq, kk, vv = (torch.randn(T, m, d, device=dev).to(torch.bfloat16) for m in (nh, nkv, nkv))
+    ctx = torch.empty((T, nh * d), dtype=torch.bfloat16, device=dev)
+    c = sh["chunk"]
+    seen_chunk = sum(p % c + 1 for p in range(n)) * B
+    seen_window = sum(min(p + 1, c) for p in range(n)) * B
+    row("tcgen05 attention, chunks + capped scores + sink", _median_ms(lambda: tc.attention_prefill(
+        qq, kk, vv, batch, ctx, nh=nh, nkv=nkv, hd=d, window=None, scale=d ** -0.5, status=status, chunk=c,
+        softcap=sh["softcap"], sink=True)), flops=4.0 * seen_chunk * nh * d)
+    row("tcgen05 attention, window", _median_ms(lambda: tc.attention_prefill(
+        qq, kk, vv, batch, ctx, nh=nh, nkv=nkv, hd=d, window=c, scale=d ** -0.5, status=status)), flops=4.0 * seen_window * nh * d)
+    # ---- the recurrent mixer ------------------------------------------------------------------------------
+    h32, mu = r(T, H), torch.rand(5, H, device=dev)
+    wstate = torch.zeros((B + 2, H + I * wd), device=dev)
+    mixed = torch.empty((4, T, H), dtype=torch.bfloat16, device=dev)
+    xw = torch.empty((T, H), device=dev)
+    row("wkv_shift_mix (five blends)", _median_ms(lambda: core.wkv_shift_mix(h32, mu, wstate, batch, mixed, last32=xw)),
+        T * H * (4 + 4 * 2 + 4))
+    w1, w2t, w0 = r(16, H) / 32, r(16, I) / 4, r(I) - 1
+    decay = torch.empty((T, I), device=dev)
+    row("wkv_shift_mix with the decay (blends + two projections + exponentials)",
+        _median_ms(lambda: core.wkv_shift_mix(h32, mu, wstate, batch, mixed, decay=(w1, w2t, w0, decay))),
+        T * H * (4 + 4 * 2) + T * I * 4)
+    rr, kk2, vv2 = r(T, I) / 8, r(T, I) / 8, r(T, I)
+    o = torch.empty((T, I), device=dev)
+    u = r(wh, wd)
+    ms = _median_ms(lambda: core.wkv_scan(rr, kk2, vv2, decay, u, wstate[:, H:], batch, o, heads=wh, d=wd))
+    row("wkv_scan (4 sequences of 2,048 tokens)", ms, T * I * 4 * 5, flops=6.0 * T * I * wd)
+    out["wkv_scan (4 sequences of 2,048 tokens)"]["us_per_token_of_a_sequence"] = round(ms * 1e3 / n, 3)
+    one = G.make_batch(dev, list(range(1, 65)), [n] * 64, [1] * 64)
+    st64 = torch.zeros((66, H + I * wd), device=dev)
+    r1 = lambda: (r(64, I) / 8)
+    a1, b1, c1, d1, o1 = r1(), r1(), r1(), torch.rand(64, I, device=dev), torch.empty((64, I), device=dev)
+    row("wkv_scan (one token of 64 sequences: the state read and written)",
+        _median_ms(lambda: core.wkv_scan(a1, b1, c1, d1, u, st64[:, H:], one, o1, heads=wh, d=wd)), 64 * I * wd * 4 * 2)
+    y = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
+    gate, nw = r(T, I), r(I)
+    row("wkv_finish (head norm + gate)", _median_ms(lambda: core.wkv_finish(o, gate, nw, 1e-5, batch, y, heads=wh, d=wd)),
+        T * I * (4 + 4 + 2))
+    # ---- the gated pair in the product's epilogue ----------------------------------------------------------
+    a16 = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    wgu = (torch.randn(2 * sh["ff"], H, device=dev) / 32).to(torch.bfloat16)
+    act = torch.empty((T, sh["ff"]), dtype=torch.bfloat16, device=dev)
+    fl = 2.0 * T * 2 * sh["ff"] * H
+    row("gate|up product, clamped sigmoid epilogue", _median_ms(lambda: tc.gemm_tc(a16, wgu, act, swiglu=True, status=status,
+                                                                                 act="clamped_sigmoid", act_param=sh["limit"])), flops=fl)
+    row("gate|up product, silu epilogue", _median_ms(lambda: tc.gemm_tc(a16, wgu, act, swiglu=True, status=status)), flops=fl)
+    core.check_status(status)
+    return out
+
+
+def run_fogapel(args):
+    """``--workload fogapel``: prefill and decode of the Fogapel design at two sizes, the closest existing
+    model at equal size beside it, and the new kernels beside their counterparts.  One JSON line per
+    shape; not the benchmark record."""
+    import torch
+
+    import moe_b200
+
+    pk = peaks()
+    names = [args.shape] if args.shape in FOGAPEL_SHAPES else list(FOGAPEL_SHAPES)
+    for name in names:
+        sh = FOGAPEL_SHAPES[name]
+        V = sh["vocab"]
+        res = {"workload": "fogapel", "shape": name, "sizes": sh, "dtype": "bfloat16", "data": "synthetic, random weights",
+               "peaks": pk}
+        for label, cfg in (("fogapel", fogapel_config(sh)), ("qwen2_moe", moe_qwen_config(sh))):
+            model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            r = {"parameters": int(model.num_parameters)}
+            eng = moe_b200.Engine(model, max_tokens=64 * (512 + args.steps + 64) + 4096, max_slots=64)
+            ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
+
+            def prefill():
+                s = eng.new_sequence()
+                eng.step([s], [ids], check=False)
+                eng.release(s)
+
+            ms = _median_ms(prefill)
+            r["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3, 0)}
+            for B in (1, 8, 64):
+                slots = [eng.new_sequence() for _ in range(B)]
+                eng.step(slots, [ids[:PROMPT_LEN]] * B, check=False)
+                for i in range(args.warmup):
+                    eng.step(slots, [[i % V]] * B, check=False)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for i in range(args.steps):
+                    eng.step(slots, [[(i + 5) % V]] * B, check=False)
+                b.record()
+                torch.cuda.synchronize()
+                eng.rt.check()
+                ms = a.elapsed_time(b) / args.steps
+                r[f"decode_b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 0)}
+                for s in slots:
+                    eng.release(s)
+            res[label] = r
+            del eng, model
+            torch.cuda.empty_cache()
+        res["kernels_at_8192_tokens"] = fogapel_kernels(sh, pk)
+        print(json.dumps(res), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -646,13 +838,13 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="with --profile-step: the path whose kernels are wanted")
-    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(SUPEVIK_SHAPES), default="a2.7b",
-                    help="with --sweep: the layer sizes; with --workload supevik: one of its shapes (default: all)")
+    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(set(SUPEVIK_SHAPES) | set(FOGAPEL_SHAPES)), default="a2.7b",
+                    help="with --sweep: the layer sizes; with --workload supevik or fogapel: one of its shapes (default: all)")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
-    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik"], default=None,
+    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik", "fogapel"], default=None,
                     help="fp32-32k: the true 32-bit path at a context of 32,768; long-prompt: one bfloat16 prompt of "
-                         "--prompt-len tokens [32768] run in pieces; supevik: the Supevik design at two sizes beside the "
-                         "closest model at equal size (each prints its own line, no benchmark record)")
+                         "--prompt-len tokens [32768] run in pieces; supevik, fogapel: that design at two sizes beside "
+                         "the closest model at equal size (each prints its own line, no benchmark record)")
     ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
                                                   "and no benchmark line")
@@ -673,6 +865,8 @@ def main():
         return run_fp32_long(args)
     if args.workload == "supevik":
         return run_supevik(args)
+    if args.workload == "fogapel":
+        return run_fogapel(args)
     return run_ours(args)
 
 

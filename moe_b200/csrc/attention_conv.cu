@@ -2,7 +2,7 @@
 // values pass a short causal convolution over time:
 //
 //   conv_heads_prepare   per channel c of a token's 32-bit projection row [q heads | k heads | v heads]
-//                        y_t[c] = sum_j w[c, j] * u_(t - taps + 1 + j)[c]     (taps >= 1; 1: y = w u)
+//                        y_t[c] = sum_j w[j, c] * u_(t - taps + 1 + j)[c]     (taps >= 1; 1: y = w u)
 //                        where u of an earlier position comes from the step's own rows if that
 //                        position belongs to the step, else from the sequence's state (the last
 //                        taps - 1 projected rows before the step), and is zero before position 0.
@@ -32,7 +32,19 @@ struct ConvCommit {
 constexpr int CONV_WARPS = 8;
 constexpr int MAX_TAPS = 16;
 
-template <typename OT>
+__device__ __forceinline__ void conv_store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void conv_store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// VEC: a lane works on four neighbouring channels at a time and keeps them in registers from the
+// convolution to the store (heads of up to 256); a pair (2i, 2i + 1) lies within a lane's four.
+template <typename OT, bool VEC>
 __global__ void __launch_bounds__(CONV_WARPS * 32)
 conv_heads_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ taps_w, int taps,
                           const float* __restrict__ state, long long state_pitch, const int* __restrict__ pos,
@@ -83,6 +95,51 @@ conv_heads_prepare_kernel(const float* __restrict__ proj, int ld, const float* _
             for (int e = lane; e < D; e += 32) st_f(dst + e, 0.f);
             continue;
         }
+        if (VEC) {
+            float4 x[2];
+            float ss = 0.f;
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+                const int e = lane * 4 + it * 128;
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e < n) {
+                    const int ch = ch0 + e;
+                    if (!taps_w) {
+                        y = *reinterpret_cast<const float4*>(proj + (size_t)t * ld + ch);
+                    } else {
+                        for (int j = 0; j < taps; j++) {
+                            const int back = taps - 1 - j;
+                            if (p_int - back < 0) continue;
+                            const int r = r_in_step - back;
+                            const float4 u = *reinterpret_cast<const float4*>(
+                                r >= 0 ? proj + (size_t)(tok0 + r) * ld + ch : st + (size_t)(taps - 1 + r) * channels + ch);
+                            const float4 w = *reinterpret_cast<const float4*>(taps_w + (size_t)j * channels + ch);
+                            y.x = fmaf(w.x, u.x, y.x), y.y = fmaf(w.y, u.y, y.y), y.z = fmaf(w.z, u.z, y.z), y.w = fmaf(w.w, u.w, y.w);
+                        }
+                    }
+                    if ((is_q || is_k) && e < rot) {
+                        const float2 cs = *reinterpret_cast<const float2*>(ang + e / 2);
+                        const float2 sn = *reinterpret_cast<const float2*>(ang + half + e / 2);
+                        const float a0 = y.x, b0 = y.y, a1 = y.z, b1 = y.w;
+                        y.x = rot_lo(a0, b0, cs.x, sn.x), y.y = rot_hi(a0, b0, cs.x, sn.x);
+                        y.z = rot_lo(a1, b1, cs.y, sn.y), y.w = rot_hi(a1, b1, cs.y, sn.y);
+                    }
+                    ss = fmaf(y.x, y.x, ss), ss = fmaf(y.y, y.y, ss), ss = fmaf(y.z, y.z, ss), ss = fmaf(y.w, y.w, ss);
+                }
+                x[it] = y;
+            }
+            float inv = 1.0f;
+            if ((is_q || is_k) && unit_norm) inv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+                const int e = lane * 4 + it * 128;
+                if (e < D) {
+                    conv_store4(dst + e, x[it].x * inv, x[it].y * inv, x[it].z * inv, x[it].w * inv);
+                    if (cd) conv_store4(cd + e, x[it].x * inv, x[it].y * inv, x[it].z * inv, x[it].w * inv);
+                }
+            }
+            continue;
+        }
         // ---- the convolution ------------------------------------------------------------------
         for (int e = lane; e < n; e += 32) {
             const int ch = ch0 + e;
@@ -97,7 +154,7 @@ conv_heads_prepare_kernel(const float* __restrict__ proj, int ld, const float* _
                     const int r = r_in_step - back;
                     const float u = r >= 0 ? proj[(size_t)(tok0 + r) * ld + ch]
                                            : st[(size_t)(taps - 1 + r) * channels + ch];
-                    y = fmaf(taps_w[(size_t)ch * taps + j], u, y);
+                    y = fmaf(taps_w[(size_t)j * channels + ch], u, y);
                 }
             }
             buf[e] = y;
@@ -149,7 +206,7 @@ conv_state_update_kernel(const float* __restrict__ proj, int ld, float* __restri
 }  // namespace
 
 // proj: [T, ld] 32-bit, bias added: q heads (nh * d), k heads (nkv * d), v heads (nkv * dv).
-// taps_w: [channels, taps] 32-bit or null (no convolution); state: [slots + 1, state_pitch] 32-bit with
+// taps_w: [taps, channels] 32-bit (a tap's factors for all channels side by side) or null (no convolution); state: [slots + 1, state_pitch] 32-bit with
 // (taps - 1) * channels floats used per slot (null if taps <= 1).  q: [T, nh, D] with a token pitch of
 // ldq; k, v: [T, nkv, D] with a token pitch of ldkv.  freq: [rot / 2].
 MOE_API int moe_conv_heads_prepare(const float* proj, int ld, const float* taps_w, int taps, const float* state,
@@ -174,13 +231,22 @@ MOE_API int moe_conv_heads_prepare(const float* proj, int ld, const float* taps_
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     const dim3 grid(num_tokens, num_tokens >= 128 ? 1 : (nh + 2 * nkv + CONV_WARPS - 1) / CONV_WARPS);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-    if (out_dt == DT_F32)
-        return launch_pdl(conv_heads_prepare_kernel<float>, grid, CONV_WARPS * 32, smem, stream, proj, ld, taps_w, taps,
-                          state, state_pitch, pos, seq_of_token, cu_seqlens, slots, eps, unit_norm, freq, rot, nh, nkv,
-                          d, dv, D, (float*)q, (float*)k, (float*)v, ldq, ldkv, c, status);
-    return launch_pdl(conv_heads_prepare_kernel<__nv_bfloat16>, grid, CONV_WARPS * 32, smem, stream, proj, ld, taps_w,
-                      taps, state, state_pitch, pos, seq_of_token, cu_seqlens, slots, eps, unit_norm, freq, rot, nh, nkv,
-                      d, dv, D, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v, ldq, ldkv, c, status);
+    const size_t esz = out_dt == DT_F32 ? 4 : 2;
+    auto al = [](const void* p, size_t a) { return ((uintptr_t)p % a) == 0; };
+    const bool vec = d % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && D <= 256 && rot % 4 == 0 && ld % 4 == 0 && ldq % 4 == 0 &&
+                     ldkv % 4 == 0 && state_pitch % 4 == 0 && al(proj, 16) && al(taps_w, 16) && al(state, 16) &&
+                     al(q, 4 * esz) && al(k, 4 * esz) && al(v, 4 * esz) && al(k_cache, 4 * esz) && al(v_cache, 4 * esz);
+#define CONV(OT_, VEC_)                                                                                              \
+    return launch_pdl(conv_heads_prepare_kernel<OT_, VEC_>, grid, CONV_WARPS * 32, smem, stream, proj, ld, taps_w, taps, \
+                      state, state_pitch, pos, seq_of_token, cu_seqlens, slots, eps, unit_norm, freq, rot, nh, nkv, d,  \
+                      dv, D, (OT_*)q, (OT_*)k, (OT_*)v, ldq, ldkv, c, status)
+    if (out_dt == DT_F32) {
+        if (vec) CONV(float, true);
+        CONV(float, false);
+    }
+    if (vec) CONV(__nv_bfloat16, true);
+    CONV(__nv_bfloat16, false);
+#undef CONV
 }
 
 MOE_API int moe_conv_state_update(const float* proj, int ld, float* state, long long state_pitch, int taps,

@@ -54,7 +54,7 @@ def lib():
             "moe_conv_heads_prepare": [P, I, P, I, P, LL, P, P, P, P, F, I, P, I, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P,
                                        P, P, I, I, I, I, P, P],
             "moe_conv_state_update": [P, I, P, LL, I, I, P, P, I, P],
-            "moe_wkv_shift_mix": [P, P, I, P, LL, P, P, P, P, I, I, P, I, P, P],
+            "moe_wkv_shift_mix": [P, P, I, P, LL, P, P, P, P, I, I, P, I, P, P, P, P, I, I, P, P],
             "moe_wkv_decay": [P, P, P, I, I, I, P, P],
             "moe_wkv_scan": [P, P, P, P, LL, P, P, LL, P, P, I, I, I, P, P],
             "moe_wkv_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
@@ -346,7 +346,7 @@ def gate_pack(ctx, out, *, nh, dv, width, gate=None):
 def conv_heads_prepare(proj, batch, *, nh, nkv, d, dv, width, q, k, v, taps_w=None, state=None, eps=0.0,
                        unit_norm=False, freq=None, rot=0, commit=None, status=None):
     """From a step's 32-bit projection rows [q heads | k heads | v heads]: a causal convolution over
-    time on every channel (``taps_w`` float32 [channels, taps]; earlier rows come from the step or,
+    time on every channel (``taps_w`` float32 [taps, channels]; earlier rows come from the step or,
     before it, from ``state`` [slots + 1, >= (taps - 1) * channels]; None: no convolution), the
     rotation of pairs (2i, 2i + 1) of the first ``rot`` dimensions of query and key heads, their
     division by the head's root mean square (``unit_norm``), and the split into q [T, nh, width] and
@@ -364,9 +364,9 @@ def conv_heads_prepare(proj, batch, *, nh, nkv, d, dv, width, q, k, v, taps_w=No
     taps = 1
     if taps_w is not None:
         _chk(taps_w, "taps", torch.float32, 2)
-        taps = taps_w.shape[1]
-        if taps_w.shape[0] != channels:
-            raise KernelError("conv_heads_prepare: one row of taps per channel")
+        taps = taps_w.shape[0]
+        if taps_w.shape[1] != channels:
+            raise KernelError("conv_heads_prepare: a tap has one factor per channel")
         if taps > 1:
             _chk(state, "state", torch.float32, 2)
     if rot:
@@ -396,35 +396,51 @@ def conv_state_update(proj, state, batch, *, taps, channels):
                                     _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs, _stream()), "conv_state_update")
 
 
-def wkv_shift_mix(h32, mu, state, batch, out, last32=None):
+WKV_FUSED_RANK = 32      # widest narrow projection of the decay that ``wkv_shift_mix`` forms itself
+
+
+def wkv_shift_mix(h32, mu, state, batch, out, last32=None, decay=None):
     """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]; the row before a step's first is ``state[slot,
     :width]`` (zeros at position 0), which afterwards holds the sequence's last row of the step.
-    ``last32`` (float32 [T, width]) receives the last blend instead of ``out``."""
+    ``last32`` (float32 [T, width]) receives the last blend instead of ``out``; or ``decay=(w1, w2t, w0,
+    out)`` (w1 [rank <= 32, width], w2t [rank, inner], w0 [inner], out float32 [T, inner]) turns it into
+    exp(-exp(w0 + w2t^T tanh(w1 x))) in the same launch."""
     _chk(h32, "h", torch.float32, 2), _chk(mu, "mu", torch.float32, 2), _chk(state, "state", torch.float32, 2)
     T, W = h32.shape
     _chk(out, "out", dims=3)
-    if mu.shape[1] != W or out.shape[1:] != (T, W) or out.shape[0] < mu.shape[0] - (1 if last32 is not None else 0) \
-            or state.shape[1] < W:
+    elsewhere = 1 if (last32 is not None or decay is not None) else 0
+    if mu.shape[1] != W or out.shape[1:] != (T, W) or out.shape[0] < mu.shape[0] - elsewhere or state.shape[1] < W:
         raise KernelError("wkv_shift_mix: shapes")
     if last32 is not None:
         _chk(last32, "last32", torch.float32, 2)
-        if tuple(last32.shape) != (T, W):
+        if tuple(last32.shape) != (T, W) or decay is not None:
             raise KernelError("wkv_shift_mix: shapes")
+    w1 = w2t = w0 = dout = None
+    rank = inner = 0
+    if decay is not None:
+        w1, w2t, w0, dout = decay
+        for t in (w1, w2t, w0, dout):
+            _chk(t, "decay", torch.float32)
+        rank, inner = w1.shape[0], w2t.shape[1]
+        if (rank > WKV_FUSED_RANK or w1.shape[1] != W or w2t.shape[0] != rank or w0.numel() != inner
+                or tuple(dout.shape) != (T, inner)):
+            raise KernelError("wkv_shift_mix: the decay's shapes")
     _ok(lib().moe_wkv_shift_mix(_p(h32), _p(mu), mu.shape[0], _p(state), state.stride(0), _p(batch.seq_of_token),
                                 _p(batch.pos), _p(batch.cu_seqlens), _p(batch.slots), T, W, _p(out), _dt(out), _p(last32),
-                                _stream()),
+                                _p(w1), _p(w2t), _p(w0), rank, inner, _p(dout), _stream()),
         "wkv_shift_mix")
 
 
-def wkv_decay(low, w2, w0, out):
-    """out[t, i] = exp(-exp(w0[i] + sum_q w2[i, q] tanh(low[t, q]))): float32 throughout."""
-    _chk(low, "low", torch.float32, 2), _chk(w2, "w2", torch.float32, 2), _chk(w0, "w0", torch.float32, 1)
+def wkv_decay(low, w2t, w0, out):
+    """out[t, i] = exp(-exp(w0[i] + sum_q w2t[q, i] tanh(low[t, q]))): float32 throughout; ``w2t`` is the
+    second projection transposed, [rank, inner]."""
+    _chk(low, "low", torch.float32, 2), _chk(w2t, "w2t", torch.float32, 2), _chk(w0, "w0", torch.float32, 1)
     _chk(out, "out", torch.float32, 2)
     T, R = low.shape
-    inner = w2.shape[0]
-    if w2.shape[1] != R or w0.numel() != inner or tuple(out.shape) != (T, inner):
+    inner = w2t.shape[1]
+    if w2t.shape[0] != R or w0.numel() != inner or tuple(out.shape) != (T, inner):
         raise KernelError("wkv_decay: shapes")
-    _ok(lib().moe_wkv_decay(_p(low), _p(w2), _p(w0), T, inner, R, _p(out), _stream()), "wkv_decay")
+    _ok(lib().moe_wkv_decay(_p(low), _p(w2t), _p(w0), T, inner, R, _p(out), _stream()), "wkv_decay")
 
 
 def wkv_scan(r, k, v, w, u, state, batch, out, *, heads, d):

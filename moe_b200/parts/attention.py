@@ -213,7 +213,8 @@ class GQAttention(Part):
         self.bo = tensors[n["o_bias"]].to(torch.float32).contiguous() if self.o_bias else None
         self.taps_w = None
         if self.taps:
-            self.taps_w = torch.cat([tensors[n[r + "_conv"]].to(torch.float32) for r in ("q", "k", "v")], dim=0).contiguous()
+            # [taps, channels]: a tap's factors for all channels side by side
+            self.taps_w = torch.cat([tensors[n[r + "_conv"]].to(torch.float32) for r in ("q", "k", "v")], dim=0).t().contiguous()
         self.q_norm_w = self.k_norm_w = None
         if self.qk_norm:
             self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()

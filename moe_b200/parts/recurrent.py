@@ -18,6 +18,8 @@ feed the r, k, v and gate projections and the normed, gated output that feeds Wo
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..cache.kv import StateRequest
@@ -47,6 +49,8 @@ class WKVMixer(Part):
         if not (self.nh > 0 and 0 < self.hd <= 256):
             raise ValueError(f"wkv: {self.nh} heads of {self.hd}; the scan takes heads of up to 256")
         self.inner = self.nh * self.hd
+        # up to this many tokens a step the blends' kernel forms the decay itself
+        self.fused_decay_tokens = int(os.environ.get("MOE_B200_WKV_FUSED_DECAY_MAX", "64"))
 
     def tensors(self):
         n, W, I = self.names, self.hidden, self.inner
@@ -90,10 +94,15 @@ class WKVMixer(Part):
         dt = ws[0].dtype if all(w.dtype == ws[0].dtype for w in ws) else torch.float32
         self.w_rkvg = torch.stack([w.to(dt) for w in ws]).contiguous()          # [4, inner, hidden]
         # the decay's two small projections stay 32-bit arithmetic in both dtypes
-        self.w1 = tensors[n["w1"]].to(torch.float32).contiguous()
-        self.w2 = tensors[n["w2"]].to(torch.float32).contiguous()
-        if self.w1.shape[0] != self.w2.shape[1]:
-            raise ValueError(f"wkv: the decay's projections disagree on their inner width ({self.w1.shape[0]} and {self.w2.shape[1]})")
+        w1 = tensors[n["w1"]]
+        self.w1 = w1.to(torch.float32).contiguous()
+        self.w1_3 = None
+        if rt.is_bf16 and w1.dtype == torch.bfloat16 and self.hidden % 8 == 0:
+            self.w1_3 = torch.cat([w1, w1, w1], dim=1).contiguous()
+        w2 = tensors[n["w2"]].to(torch.float32)
+        if self.w1.shape[0] != w2.shape[1]:
+            raise ValueError(f"wkv: the decay's projections disagree on their inner width ({self.w1.shape[0]} and {w2.shape[1]})")
+        self.w2t = w2.t().contiguous()                 # [rank, inner]: the decay kernel reads it by columns
         self.rank = int(self.w1.shape[0])
         self.w0 = tensors[n["w0"]].to(torch.float32).contiguous()
         self.u = tensors[n["u"]].to(torch.float32).contiguous()
@@ -112,16 +121,31 @@ class WKVMixer(Part):
         T, W, I = batch.num_tokens, self.hidden, self.inner
         dev = h.f32.device
         # ---- the five blends (and the state's last-token row) -----------------------------------
-        mixed = rt.empty((4, T, W))
-        xw = torch.empty((T, W), dtype=torch.float32, device=dev)       # the decay's blend stays 32-bit
-        core.wkv_shift_mix(h.f32, self.mu, state, batch, mixed, last32=xw)
+        decay = torch.empty((T, I), dtype=torch.float32, device=dev)
+        if self.rank <= core.WKV_FUSED_RANK and T <= self.fused_decay_tokens:
+            # few tokens: the decay exp(-exp(W2 tanh(W1 x_w) + w0)) in the same launch, its blend in registers
+            mixed = rt.empty((4, T, W))
+            core.wkv_shift_mix(h.f32, self.mu, state, batch, mixed, decay=(self.w1, self.w2t, self.w0, decay))
+        else:
+            # many tokens: every block of the fused form would read both projections from L2 (measured
+            # 833 us against 104 + 40 + 84 at 8,192 tokens of width 2,048).  The blend stays 32-bit; in
+            # bfloat16 its narrow projection runs on the tensor cores without leaving 32-bit accuracy: the
+            # blend as three bfloat16 terms (exact) against the (bfloat16, hence exact) rows, three times
+            # side by side, accumulated in float32
+            mixed = rt.empty((4, T, W))
+            xw = torch.empty((T, W), dtype=torch.float32, device=dev)
+            core.wkv_shift_mix(h.f32, self.mu, state, batch, mixed, last32=xw)
+            low = torch.empty((T, self.rank), dtype=torch.float32, device=dev)
+            done = False
+            if self.w1_3 is not None:
+                from ..ops import tc
+
+                done = tc.gemm_tc(core.split3(xw), self.w1_3, low, bn=64, splits=8, status=rt.status)
+            if not done:
+                core.gemm_generic(xw, self.w1, low, status=rt.status)
+            core.wkv_decay(low, self.w2t, self.w0, decay)
         # ---- r, k, v and the gate: one grouped product, a group a blend ---------------------------
         rkvg = grouped_linear(rt, mixed.view(4 * T, W), self.w_rkvg, self._group_offsets(T, dev), 4 * T)
-        # ---- the decay exp(-exp(W2 tanh(W1 x_w) + w0)), 32-bit -------------------------------------
-        low = torch.empty((T, self.rank), dtype=torch.float32, device=dev)
-        core.gemm_generic(xw, self.w1, low, status=rt.status)
-        decay = torch.empty((T, I), dtype=torch.float32, device=dev)
-        core.wkv_decay(low, self.w2, self.w0, decay)
         # ---- the scan over each sequence's tokens -----------------------------------------------
         o = torch.empty((T, I), dtype=torch.float32, device=dev)
         core.wkv_scan(rkvg[:T], rkvg[T:2 * T], rkvg[2 * T:3 * T], decay, self.u, state[:, W:], batch, o,

@@ -127,7 +127,7 @@ def test_convolution_rotation_of_pairs_unit_norm_and_split_in_pieces(bf16, nh, n
         T = rows.shape[0]
         q, k, v = (torch.full((T, n, D), 7.0, dtype=dt, device="cuda") for n in (nh, nkv, nkv))
         core.conv_heads_prepare(rows, batch, nh=nh, nkv=nkv, d=d, dv=dv, width=D, q=q, k=k, v=v,
-                                taps_w=dev(taps_w) if taps else None, state=state if taps > 1 else None, eps=eps,
+                                taps_w=dev(taps_w.t()) if taps else None, state=state if taps > 1 else None, eps=eps,
                                 unit_norm=unit, freq=freq, rot=rot, status=status)
         if taps > 1:
             core.conv_state_update(rows, state, batch, taps=taps, channels=ch)
@@ -152,10 +152,15 @@ def test_convolution_rotation_of_pairs_unit_norm_and_split_in_pieces(bf16, nh, n
 
 
 @pytest.mark.parametrize("bf16", [False, True])
-@pytest.mark.parametrize("heads,d,W,rank", [(2, 32, 64, 5), (1, 40, 48, 3), (3, 8, 32, 1), (2, 64, 128, 8), (2, 128, 64, 4), (4, 20, 24, 2)])
-def test_recurrent_mixer_kernels_in_pieces_with_the_state_carried(bf16, heads, d, W, rank):
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("heads,d,W,rank", [(2, 32, 64, 5), (1, 40, 48, 3), (3, 8, 32, 1), (2, 64, 128, 8), (2, 128, 64, 32), (4, 20, 24, 2),
+                                            (2, 16, 40, 40), (1, 200, 32, 4)])
+def test_recurrent_mixer_kernels_in_pieces_with_the_state_carried(bf16, fused, heads, d, W, rank):
     """Blends, decay, scan and the normed, gated output, for two sequences cut into unequal pieces
-    (one token, two, many), against the plain loop over whole sequences."""
+    (one token, two, many), against the plain loop over whole sequences.  The decay is formed in the
+    blends' launch (``fused``, a narrow projection of up to 32) or by kernels of its own."""
+    if fused and rank > 32:
+        pytest.skip("the blends' kernel forms the decay for a narrow projection of up to 32")
     from moe_b200.ops import core
 
     g = torch.Generator().manual_seed(heads * 1000 + d)
@@ -176,12 +181,15 @@ def test_recurrent_mixer_kernels_in_pieces_with_the_state_carried(bf16, heads, d
         x = dev(torch.cat([h[s][a:b] for s, a, b in step]))
         T = x.shape[0]
         mixed = torch.empty((4, T, W), dtype=dt, device="cuda")
-        xw = torch.empty((T, W), device="cuda")
-        core.wkv_shift_mix(x, dev(mu), state, batch, mixed, last32=xw)
-        r, k, v, gl = (dev(mixed[i].double().cpu() @ Wm[s].double().T) for i, s in enumerate("rkvg"))
-        low = dev(xw.double().cpu() @ w1.double().T)
         decay = torch.empty((T, I), device="cuda")
-        core.wkv_decay(low, dev(w2), dev(w0), decay)
+        if fused:
+            core.wkv_shift_mix(x, dev(mu), state, batch, mixed, decay=(dev(w1), dev(w2.t()), dev(w0), decay))
+        else:
+            xw = torch.empty((T, W), device="cuda")
+            core.wkv_shift_mix(x, dev(mu), state, batch, mixed, last32=xw)
+            low = dev(xw.double().cpu() @ w1.double().T)
+            core.wkv_decay(low, dev(w2.t()), dev(w0), decay)
+        r, k, v, gl = (dev(mixed[i].double().cpu() @ Wm[s].double().T) for i, s in enumerate("rkvg"))
         o = torch.empty((T, I), device="cuda")
         core.wkv_scan(r, k, v, decay, dev(u), state[:, W:], batch, o, heads=heads, d=d)
         y = torch.empty((T, I), dtype=dt, device="cuda")
