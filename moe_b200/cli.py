@@ -24,7 +24,7 @@ import time
 from typing import Dict, List, Tuple
 
 USAGE = """\
-moe - Qwen2 MoE generation on one B200
+moe - generation on one B200 (Qwen2 MoE, Supevik, Fogapel)
 
 USAGE
   moe run   <model> [options]        generate tokens
@@ -233,7 +233,7 @@ def tracing_parts(model):
     """(layer index, feed-forward part) for every run of a layer, in the order of the schedule.  A part
     that routes records its decisions in its ``trace`` list when that is set (``Part.trace``); one that
     does not leaves the list empty."""
-    return [(e.layer, model.blocks[e.layer].ffn) for e in model.spec.schedule]
+    return [(e.layer, model.blocks[e.layer].ffn) for e in model.spec.schedule if model.blocks[e.layer].ffn is not None]
 
 
 def write_trace(path: str, model, runs, tokens) -> int:
