@@ -58,7 +58,8 @@ class PostNormDelta(LazyDelta):
 class ScaledPairDelta(LazyDelta):
     """The outputs a and b of two sublayers that read the same input (b may be None), each still to
     be multiplied by a per-channel factor: delta = a * sa + b * sb.  An RMS norm forms the sum, the
-    residual sum and itself in one kernel."""
+    residual sum and itself in one kernel.  b may itself be a delta not computed yet (routed experts'
+    outputs before their combine), which that kernel forms too if it knows the kind."""
 
     kind = "scaled_pair"
 
@@ -68,7 +69,8 @@ class ScaledPairDelta(LazyDelta):
     def materialize(self, rt) -> torch.Tensor:
         out = self.a * self.sa
         if self.b is not None:
-            out.addcmul_(self.b, self.sb)
+            b = self.b.materialize(rt) if isinstance(self.b, LazyDelta) else self.b
+            out.addcmul_(b, self.sb)
         return out
 
 

@@ -118,8 +118,9 @@ class ParallelBlock:
         a = self.mixer.forward(rt, h, batch, cache_view, state)
         if self.ffn is None:
             return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a))
-        b = self.ffn.forward(rt, h, batch)
-        return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a), b, self._factor(rt, self.scale2, b))
+        # (a feed-forward may hand its output on uncombined, for the next norm to finish: base.LazyDelta)
+        b = getattr(self.ffn, "forward_lazy", self.ffn.forward)(rt, h, batch)
+        return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a), b, self._factor(rt, self.scale2, a))
 
 
 _BLOCKS = {"prenorm": PreNormBlock, "sandwich": SandwichBlock, "parallel": ParallelBlock}

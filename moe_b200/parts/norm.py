@@ -56,8 +56,15 @@ class RMSNorm(Part):
             out32 = rt.empty((n, self.size), torch.float32)
         if isinstance(delta, LazyDelta) and delta.kind == "scaled_pair":
             # two sublayers' outputs times their per-channel factors, the residual sum and the norm
-            core.rmsnorm_scaled(x, delta.a, delta.sa, delta.b, delta.sb, self.weight, self.eps, rows=rows, out32=out32,
-                                out16=out16, write_back=write_back, status=rt.status)
+            b, combine = delta.b, None
+            if isinstance(b, LazyDelta):
+                if b.kind == "expert_combine" and b.shared_gate is None:
+                    # the experts' combine inside this kernel too
+                    b, combine = None, (b.y, b.pos_of_pair, b.topk_w, b.top_k, b.shared)
+                else:
+                    b = b.materialize(rt)
+            core.rmsnorm_scaled(x, delta.a, delta.sa, b, delta.sb, self.weight, self.eps, rows=rows, out32=out32,
+                                out16=out16, write_back=write_back, status=rt.status, combine=combine)
             return Activations(act=out16 if rt.is_bf16 else out32, f32=out32)
         if isinstance(delta, LazyDelta):
             if delta.kind != "expert_combine" or not core.rmsnorm_combine(

@@ -238,6 +238,21 @@ def test_norm_with_two_scaled_sublayer_outputs_in_front(H, bf16):
         else:
             assert (xs.cpu().double() - s).abs().max() < 1e-5     # the sum went back into the stream
         assert (out.double().cpu() - ref).abs().max() < (3e-2 if bf16 else 5e-6)
+    # the second output still as routed experts left it: three picks a token (one of them none), a shared expert
+    y, shared, wt = torch.randn(3 * T, H, generator=g), torch.randn(T, H, generator=g), torch.rand(T, 3, generator=g)
+    pos = torch.randperm(3 * T, generator=g).reshape(T, 3).to(torch.int32)
+    pos[2, 1] = -1
+    for with_shared in (True, False):
+        xs = dev(x)
+        out = torch.empty((T, H), dtype=torch.bfloat16 if bf16 else torch.float32, device="cuda")
+        core.rmsnorm_scaled(xs, dev(a), dev(sa), None, dev(sb), dev(w), 1e-5, status=status,
+                            combine=(dev(y), pos.cuda(), dev(wt), 3, dev(shared) if with_shared else None),
+                            **{"out16" if bf16 else "out32": out})
+        comb = sum(torch.where(pos[:, j:j + 1] >= 0, wt[:, j:j + 1].double() * y.double()[pos[:, j].clamp(min=0).long()], 0.0)
+                   for j in range(3)) + (shared.double() if with_shared else 0.0)
+        s = x.double() + a.double() * sa.double() + comb * sb.double()
+        assert (xs.cpu().double() - s).abs().max() < 1e-5
+        assert (out.double().cpu() - plain.unit_rms(s, 1e-5) * w.double()).abs().max() < (3e-2 if bf16 else 5e-6)
     core.check_status(status)
 
 
